@@ -1,0 +1,205 @@
+"""ctypes view of the C ABI in include/cwarp_rnnt_b200.h, operating on torch CUDA tensors by raw pointer.
+
+This is the same boundary a foreign-language binding would use: every call passes plain device pointers, sizes and the
+current CUDA stream. There is no fallback: if the CUDA library has not been built the import of :func:`lib` raises.
+"""
+import ctypes
+import os
+from typing import Optional
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libcwarp_rnnt_b200.so")
+
+F32, F16, BF16, F64 = 0, 1, 2, 3
+FUSED_LOG_SOFTMAX, COSTS_ONLY, REDUCE_MEAN, REDUCE_SUM, AVERAGE_FRAMES = 0x01, 0x02, 0x04, 0x08, 0x10
+ST_BAD_LENGTH, ST_ROW_MISMATCH, ST_BAD_LABEL, ST_FWD_BWD_GAP = 0x01, 0x02, 0x04, 0x08
+MAX_COLUMNS = 4096
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}
+
+EXPORTS = [
+    "cwrnnt_abi_version", "cwrnnt_status_string", "cwrnnt_last_error", "cwrnnt_workspace_bytes", "cwrnnt_forward",
+    "cwrnnt_backward", "cwrnnt_pair_grads", "cwrnnt_export_alpha_beta", "cwrnnt_scatter_scratch_bytes",
+    "cwrnnt_scatter_backward", "cwrnnt_read_status", "cwrnnt_host_ctx_create", "cwrnnt_host_ctx_destroy",
+    "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host",
+]
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [("n_rows", ctypes.c_int64), ("V", ctypes.c_int32), ("B", ctypes.c_int32),
+                ("y_stride", ctypes.c_int32), ("max_u", ctypes.c_int32), ("blank", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("flags", ctypes.c_int32), ("mean_denominator", ctypes.c_int32)]
+
+
+class CwrnntError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.isfile(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m compactwarprnntloss_b200.build` "
+                              "(there is no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        pp = ctypes.POINTER(Problem)
+        L.cwrnnt_abi_version.restype = ctypes.c_int
+        L.cwrnnt_status_string.restype = ctypes.c_char_p
+        L.cwrnnt_status_string.argtypes = [ctypes.c_int]
+        L.cwrnnt_last_error.restype = ctypes.c_char_p
+        L.cwrnnt_workspace_bytes.restype = i64
+        L.cwrnnt_workspace_bytes.argtypes = [pp]
+        L.cwrnnt_forward.argtypes = [pp, vp, vp, vp, vp, vp, i64, vp, vp, vp]
+        L.cwrnnt_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
+        L.cwrnnt_pair_grads.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
+        L.cwrnnt_export_alpha_beta.argtypes = [pp, vp, vp, vp, i32, i32, vp, vp, vp]
+        L.cwrnnt_scatter_scratch_bytes.restype = i64
+        L.cwrnnt_scatter_scratch_bytes.argtypes = [i32]
+        L.cwrnnt_scatter_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i64, vp, vp]
+        L.cwrnnt_read_status.argtypes = [vp, ctypes.POINTER(i32 * 4), vp]
+        L.cwrnnt_host_ctx_create.argtypes = [ctypes.POINTER(vp)]
+        L.cwrnnt_host_ctx_destroy.argtypes = [vp]
+        L.cwrnnt_host_ctx_destroy.restype = None
+        L.cwrnnt_host_ctx_error.restype = ctypes.c_char_p
+        L.cwrnnt_host_ctx_error.argtypes = [vp]
+        L.cwrnnt_loss_grad_host.argtypes = [vp, pp, vp, vp, vp, vp, vp, i32, vp, vp, vp, i64, ctypes.POINTER(i32 * 4)]
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str = "cwrnnt") -> None:
+    if status != 0:
+        L = lib()
+        msg = L.cwrnnt_status_string(status).decode()
+        if status == 4:
+            msg += ": " + L.cwrnnt_last_error().decode()
+        raise CwrnntError(f"{what}: {msg} (status {status})")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt not in _DTYPES:
+        raise TypeError(f"unsupported logits dtype {dt}; expected float32, float16, bfloat16 or float64")
+    return _DTYPES[dt]
+
+
+def cost_dtype(dt: torch.dtype) -> torch.dtype:
+    return torch.float64 if dt == torch.float64 else torch.float32
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def make_problem(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, blank: int, flags: int,
+                 mean_denominator: int = 0, max_u: Optional[int] = None) -> Problem:
+    ys = y.size(1) if y.dim() == 2 else 0
+    return Problem(n_rows=x.size(0), V=x.size(1), B=lx.numel(), y_stride=ys, max_u=ys if max_u is None else max_u,
+                   blank=blank, dtype=dtype_code(x.dtype), flags=flags, mean_denominator=mean_denominator)
+
+
+def workspace_bytes(p: Problem) -> int:
+    n = lib().cwrnnt_workspace_bytes(ctypes.byref(p))
+    if n < 0:
+        raise CwrnntError("invalid problem description")
+    return int(n)
+
+
+def alloc_workspace(p: Problem, device) -> torch.Tensor:
+    # torch's caching allocator hands out 512-byte aligned blocks; the ABI needs 256
+    return torch.empty(workspace_bytes(p), dtype=torch.uint8, device=device)
+
+
+def forward(p: Problem, x, lx, ly, y, workspace, costs, loss=None) -> None:
+    with torch.cuda.device(x.device):
+        check(lib().cwrnnt_forward(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
+                                   workspace.numel(), _ptr(costs), _ptr(loss), _stream(x.device)), "cwrnnt_forward")
+
+
+def backward(p: Problem, x, lx, ly, y, workspace, grad_costs, grad_costs_stride, grad_x) -> None:
+    with torch.cuda.device(x.device):
+        check(lib().cwrnnt_backward(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
+                                    _ptr(grad_costs), grad_costs_stride, _ptr(grad_x), _stream(x.device)),
+              "cwrnnt_backward")
+
+
+def pair_grads(p: Problem, x, lx, ly, y, workspace, grads) -> None:
+    with torch.cuda.device(grads.device):
+        check(lib().cwrnnt_pair_grads(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
+                                      _ptr(grads), _stream(grads.device)), "cwrnnt_pair_grads")
+
+
+def export_alpha_beta(p: Problem, lx, ly, workspace, t_max, u_max1, alphas, betas) -> None:
+    with torch.cuda.device(lx.device):
+        check(lib().cwrnnt_export_alpha_beta(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(workspace), t_max, u_max1,
+                                             _ptr(alphas), _ptr(betas), _stream(lx.device)),
+              "cwrnnt_export_alpha_beta")
+
+
+def scatter_backward(p: Problem, grads, grad_costs, lx, ly, y, dense) -> None:
+    n = lib().cwrnnt_scatter_scratch_bytes(p.B)
+    scratch = torch.empty(n, dtype=torch.uint8, device=grads.device)
+    with torch.cuda.device(grads.device):
+        check(lib().cwrnnt_scatter_backward(ctypes.byref(p), _ptr(grads), _ptr(grad_costs), _ptr(lx), _ptr(ly),
+                                            _ptr(y), _ptr(scratch), n, _ptr(dense), _stream(grads.device)),
+              "cwrnnt_scatter_backward")
+
+
+def read_status(workspace: torch.Tensor):
+    out = (ctypes.c_int32 * 4)()
+    with torch.cuda.device(workspace.device):
+        check(lib().cwrnnt_read_status(_ptr(workspace), ctypes.byref(out), _stream(workspace.device)),
+              "cwrnnt_read_status")
+    return list(out)
+
+
+class HostPipeline:
+    """Host-buffer entry point (cwrnnt_loss_grad_host): CPU tensors in, CPU tensors out, chunked over PCIe."""
+
+    def __init__(self, device=0):
+        self.device = torch.device("cuda", device) if not isinstance(device, torch.device) else device
+        self._ctx = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream()  # make sure the primary context exists
+            check(lib().cwrnnt_host_ctx_create(ctypes.byref(self._ctx)), "cwrnnt_host_ctx_create")
+
+    def close(self):
+        if self._ctx:
+            lib().cwrnnt_host_ctx_destroy(self._ctx)
+            self._ctx = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def run(self, x, lx, ly, y, blank=0, flags=FUSED_LOG_SOFTMAX, grad_costs=None, grad_x=None, chunk_rows=0,
+            mean_denominator=0):
+        """All tensors on the CPU (pin them for overlap). Returns (costs, loss or None, status words)."""
+        assert not x.is_cuda and x.is_contiguous()
+        p = make_problem(x, lx, y, blank, flags, mean_denominator)
+        ct = cost_dtype(x.dtype)
+        costs = torch.empty(p.B, dtype=ct)
+        loss = torch.zeros((), dtype=ct) if flags & (REDUCE_MEAN | REDUCE_SUM) else None
+        st = (ctypes.c_int32 * 4)()
+        stride = 0
+        if grad_costs is not None:
+            grad_costs = grad_costs.to(ct).contiguous()
+            stride = 0 if grad_costs.numel() == 1 else 1
+        rc = lib().cwrnnt_loss_grad_host(self._ctx, ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly),
+                                         _ptr(y) if y.numel() else None, _ptr(grad_costs), stride, _ptr(costs),
+                                         _ptr(loss), _ptr(grad_x), chunk_rows, ctypes.byref(st))
+        if rc == 4:
+            raise CwrnntError("cwrnnt_loss_grad_host: " + lib().cwrnnt_host_ctx_error(self._ctx).decode())
+        check(rc, "cwrnnt_loss_grad_host")
+        return costs, loss, list(st)

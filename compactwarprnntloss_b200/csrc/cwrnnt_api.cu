@@ -1,0 +1,165 @@
+// C ABI of the engine (include/cwarp_rnnt_b200.h): argument checks, workspace carving, kernel sequencing.
+// No allocation, no synchronisation (except cwrnnt_read_status), no exceptions.
+#include <cstdio>
+#include <cstring>
+
+#include "cwrnnt_kernels.h"
+
+using namespace cwrnnt;
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int fail_launch(const char *what, cudaError_t e)
+{
+    std::snprintf(g_last_error, sizeof g_last_error, "%s: %s", what, cudaGetErrorString(e));
+    return CWRNNT_ERR_LAUNCH;
+}
+
+int check_problem(const cwrnnt_problem *p)
+{
+    if (!p) return CWRNNT_ERR_ARGUMENT;
+    if (p->n_rows < 0 || p->V < 1 || p->B < 0 || p->max_u < 0 || p->y_stride < p->max_u) return CWRNNT_ERR_ARGUMENT;
+    if (p->blank < 0 || p->blank >= p->V) return CWRNNT_ERR_ARGUMENT;
+    if (p->dtype < CWRNNT_F32 || p->dtype > CWRNNT_F64) return CWRNNT_ERR_ARGUMENT;
+    if (p->mean_denominator < 0) return CWRNNT_ERR_ARGUMENT;
+    const int known = CWRNNT_FUSED_LOG_SOFTMAX | CWRNNT_COSTS_ONLY | CWRNNT_REDUCE_MEAN | CWRNNT_REDUCE_SUM |
+                      CWRNNT_AVERAGE_FRAMES;
+    if (p->flags & ~known) return CWRNNT_ERR_ARGUMENT;
+    if ((p->flags & CWRNNT_REDUCE_MEAN) && (p->flags & CWRNNT_REDUCE_SUM)) return CWRNNT_ERR_ARGUMENT;
+    if (p->max_u + 1 > CWRNNT_MAX_COLUMNS) return CWRNNT_ERR_UNSUPPORTED;
+    return CWRNNT_OK;
+}
+
+int check_workspace(const cwrnnt_problem *p, const void *ws, int64_t bytes, Workspace *w)
+{
+    if (!ws || reinterpret_cast<uintptr_t>(ws) % 256 != 0) return CWRNNT_ERR_WORKSPACE;
+    const int64_t need = carve_workspace(p->n_rows, p->B, const_cast<void *>(ws), w);
+    if (bytes >= 0 && bytes < need) return CWRNNT_ERR_WORKSPACE;
+    return CWRNNT_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int cwrnnt_abi_version(void) { return CWRNNT_ABI_VERSION; }
+
+const char *cwrnnt_status_string(int status)
+{
+    switch (status) {
+    case CWRNNT_OK: return "ok";
+    case CWRNNT_ERR_ARGUMENT: return "invalid argument";
+    case CWRNNT_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case CWRNNT_ERR_UNSUPPORTED: return "label length above the supported maximum";
+    case CWRNNT_ERR_LAUNCH: return "CUDA launch or runtime failure";
+    }
+    return "unknown status";
+}
+
+const char *cwrnnt_last_error(void) { return g_last_error; }
+
+int64_t cwrnnt_workspace_bytes(const cwrnnt_problem *p)
+{
+    if (check_problem(p) != CWRNNT_OK) return -1;
+    return carve_workspace(p->n_rows, p->B, nullptr, nullptr);
+}
+
+int cwrnnt_forward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                   void *workspace, int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (!lx || !ly || !costs || (p->n_rows > 0 && !x) || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, workspace_bytes, &w);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if ((e = launch_prep(*p, lx, ly, w, costs, s)) != cudaSuccess) return fail_launch("prep", e);
+    if ((e = launch_gather(*p, x, lx, ly, y, w, s)) != cudaSuccess) return fail_launch("gather", e);
+    if ((e = launch_wavefront(*p, lx, ly, w, costs, loss, s)) != cudaSuccess) return fail_launch("wavefront", e);
+    return CWRNNT_OK;
+}
+
+int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                    const void *workspace, const void *grad_costs, int32_t grad_costs_stride, void *grad_x,
+                    cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->flags & CWRNNT_COSTS_ONLY) return CWRNNT_ERR_ARGUMENT;  // that forward kept no alpha
+    if (!lx || !ly || (p->n_rows > 0 && (!x || !grad_x)) || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
+    if (grad_costs_stride != 0 && grad_costs_stride != 1) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, -1, &w);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    cudaError_t e = launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x,
+                                reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("grad", e);
+}
+
+int cwrnnt_pair_grads(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                      const void *workspace, void *grads, cwrnnt_stream_t stream)
+{
+    (void)x;
+    (void)y;
+    int st = check_problem(p);
+    if (st) return st;
+    if ((p->flags & CWRNNT_COSTS_ONLY) || !lx || !ly || (p->n_rows > 0 && !grads)) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, -1, &w);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    cudaError_t e = launch_pair_grads(*p, lx, ly, w, grads, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("pair_grads", e);
+}
+
+int cwrnnt_export_alpha_beta(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const void *workspace,
+                             int32_t t_max, int32_t u_max1, void *alphas, void *betas, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (!lx || !ly || t_max < 0 || u_max1 < 0) return CWRNNT_ERR_ARGUMENT;
+    if ((p->flags & CWRNNT_COSTS_ONLY) && alphas) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, -1, &w);
+    if (st) return st;
+    if (p->B == 0 || (!alphas && !betas)) return CWRNNT_OK;
+    cudaError_t e = launch_export_ab(*p, lx, ly, w, t_max, u_max1, alphas, betas,
+                                     reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("export_alpha_beta", e);
+}
+
+int64_t cwrnnt_scatter_scratch_bytes(int32_t B) { return B < 0 ? -1 : align_up(8 * (int64_t(B) + 1), 256); }
+
+int cwrnnt_scatter_backward(const cwrnnt_problem *p, const void *grads, const void *grad_costs, const int32_t *lx,
+                            const int32_t *ly, const int32_t *y, void *scratch, int64_t scratch_bytes, void *dense,
+                            cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->dtype != CWRNNT_F32 && p->dtype != CWRNNT_F64) return CWRNNT_ERR_ARGUMENT;
+    if (!lx || !ly || !grad_costs || (p->n_rows > 0 && (!grads || !dense)) || (p->max_u > 0 && !y))
+        return CWRNNT_ERR_ARGUMENT;
+    if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 8 != 0 || scratch_bytes < cwrnnt_scatter_scratch_bytes(p->B))
+        return CWRNNT_ERR_WORKSPACE;
+    if (p->B == 0) return CWRNNT_OK;
+    cudaError_t e = launch_scatter(*p, grads, grad_costs, lx, ly, y, static_cast<int64_t *>(scratch), dense,
+                                   reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("scatter_backward", e);
+}
+
+int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream)
+{
+    if (!workspace || !out) return CWRNNT_ERR_ARGUMENT;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(out, workspace, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("read_status", e);
+}
+
+}  // extern "C"

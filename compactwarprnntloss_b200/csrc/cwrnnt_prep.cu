@@ -1,0 +1,109 @@
+// K0 - per-call preparation in one CTA: row offsets (exclusive prefix sum of T_n*(U_n+1), 64-bit), input
+// validation into the status words, and the longest-critical-path-first order used by the wavefront kernel.
+// Replaces the five ATen launches that build `offset` in the reference (cwarp_cuda.cpp:98-103) and the host-side
+// max().item() synchronisations (cwarp_cuda_rnnt_kernel.cu:395-396, cwarp_cuda_gather_kernel.cu:85-86).
+#include "cwrnnt_kernels.h"
+
+namespace cwrnnt {
+
+constexpr int kPrepThreads = 1024;
+constexpr int kSortLimit = 4096;  // rank sort is O(B^2 / threads); beyond this the order is the identity
+
+template <typename CostT>
+__global__ void __launch_bounds__(kPrepThreads)
+prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int B, int64_t n_rows, int max_u,
+            Workspace w, CostT *__restrict__ costs, int64_t *off_only)
+{
+    __shared__ int64_t part[kPrepThreads];
+    __shared__ int bad_first;
+    __shared__ int keys[kSortLimit];
+    const int tid = threadIdx.x;
+    int64_t *off = off_only ? off_only : w.off;
+    if (tid == 0) bad_first = 0x7fffffff;
+    __syncthreads();
+
+    // contiguous slice per thread -> local sums -> block scan -> offsets
+    const int per = (B + kPrepThreads - 1) / kPrepThreads;
+    const int beg = min(tid * per, B), end = min(beg + per, B);
+    int64_t local = 0;
+    for (int n = beg; n < end; ++n) {
+        int T = lx[n], U = ly[n];
+        if (T < 1 || U < 0 || U > max_u) {
+            atomicMin(&bad_first, n);
+            T = T < 1 ? 1 : T;
+            U = U < 0 ? 0 : (U > max_u ? max_u : U);
+        }
+        local += int64_t(T) * (int64_t(U) + 1);
+    }
+    part[tid] = local;
+    __syncthreads();
+    for (int step = 1; step < kPrepThreads; step <<= 1) {
+        int64_t add = tid >= step ? part[tid - step] : 0;
+        __syncthreads();
+        part[tid] += add;
+        __syncthreads();
+    }
+    int64_t run = part[tid] - local;  // exclusive prefix of this thread's slice
+    for (int n = beg; n < end; ++n) {
+        int T = lx[n], U = ly[n];
+        T = T < 1 ? 1 : T;
+        U = U < 0 ? 0 : (U > max_u ? max_u : U);
+        off[n] = run;
+        run += int64_t(T) * (int64_t(U) + 1);
+    }
+    const int64_t total = part[kPrepThreads - 1];
+    if (tid == 0) off[B] = total;
+    if (off_only) return;
+
+    int st = 0;
+    if (bad_first != 0x7fffffff) st |= CWRNNT_ST_BAD_LENGTH;
+    if (total != n_rows) st |= CWRNNT_ST_ROW_MISMATCH;
+    if (tid == 0) {
+        w.status[0] = st;
+        w.status[1] = bad_first != 0x7fffffff ? bad_first : -1;
+        w.status[2] = int(total & 0x7fffffff);
+        w.status[3] = 0;
+        *w.ticket = 0u;
+    }
+    if (st & CWRNNT_ST_FATAL) {
+        // nothing downstream runs; make that visible in the result
+        for (int n = tid; n < B; n += kPrepThreads) costs[n] = CostT(NAN);
+        return;
+    }
+
+    // longest wavefront first: key = T+U, ties by index (stable, deterministic)
+    if (B <= kSortLimit) {
+        for (int n = tid; n < B; n += kPrepThreads) keys[n] = lx[n] + ly[n];
+        __syncthreads();
+        for (int n = tid; n < B; n += kPrepThreads) {
+            const int k = keys[n];
+            int rank = 0;
+            for (int j = 0; j < B; ++j) rank += (keys[j] > k) || (keys[j] == k && j < n);
+            w.order[rank] = n;
+        }
+    } else {
+        for (int n = tid; n < B; n += kPrepThreads) w.order[n] = n;
+    }
+}
+
+cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
+                        void *costs, cudaStream_t s)
+{
+    if (p.dtype == CWRNNT_F64)
+        prep_kernel<double><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
+                                                       static_cast<double *>(costs), nullptr);
+    else
+        prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
+                                                      static_cast<float *>(costs), nullptr);
+    return cudaGetLastError();
+}
+
+// Offsets only (reference-shaped scatter backward recomputes them, cwarp_cuda.cpp:124-129).
+cudaError_t launch_offsets_only(const int32_t *lx, const int32_t *ly, int B, int max_u, int64_t *off, cudaStream_t s)
+{
+    Workspace none{};
+    prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, B, 0, max_u, none, nullptr, off);
+    return cudaGetLastError();
+}
+
+}  // namespace cwrnnt

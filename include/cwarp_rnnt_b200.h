@@ -1,0 +1,183 @@
+/*
+ * cwarp_rnnt_b200 - C ABI of the B200 (sm_100a) RNN-T loss engine for compact-layout inputs.
+ *
+ * This is the boundary a binding of the reference project (maxwellzh/CompactWarpRNNTLoss) targets instead of its own
+ * CUDA host functions. Plain pointers and sizes only: no torch types, no exceptions. Unless a comment says otherwise,
+ * every pointer is a DEVICE pointer valid on the device that is current at the call, every call is asynchronous on
+ * `stream`, performs no allocation and no host synchronisation, and returns a cwrnnt_status (0 = launched).
+ *
+ * Data layout ("compact", reference test/test.py:34-48, cwarp_cuda_gather_kernel.cu:36, cwarp_cuda.cpp:72-77):
+ * sequence n owns rows [offset[n], offset[n] + T_n*(U_n+1)) of the row-major [n_rows, V] matrix, rows ordered (t,u)
+ * row-major; offset = exclusive prefix sum of T_n*(U_n+1). Labels are a padded row-major int32 [B, y_stride] matrix
+ * of which only y[n][u], u < U_n, is read. T_n = lx[n] >= 1, U_n = ly[n] >= 0.
+ */
+#ifndef CWARP_RNNT_B200_H
+#define CWARP_RNNT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CWRNNT_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define CWRNNT_API __attribute__((visibility("default")))
+#else
+#define CWRNNT_API
+#endif
+
+typedef struct CUstream_st *cwrnnt_stream_t; /* same type as cudaStream_t */
+
+typedef enum {
+    CWRNNT_F32 = 0,  /* float logits, float costs and gradients                         */
+    CWRNNT_F16 = 1,  /* __half logits and gradients, float math and costs               */
+    CWRNNT_BF16 = 2, /* __nv_bfloat16 logits and gradients, float math and costs        */
+    CWRNNT_F64 = 3   /* double logits, costs and gradients (the reference's other type) */
+} cwrnnt_dtype;
+
+typedef enum {
+    CWRNNT_OK = 0,
+    CWRNNT_ERR_ARGUMENT = 1,   /* null pointer, negative size, blank outside [0,V), unknown dtype or flag */
+    CWRNNT_ERR_WORKSPACE = 2,  /* workspace pointer misaligned or smaller than cwrnnt_workspace_bytes()   */
+    CWRNNT_ERR_UNSUPPORTED = 3,/* max_u + 1 above CWRNNT_MAX_COLUMNS                                      */
+    CWRNNT_ERR_LAUNCH = 4      /* a CUDA launch or runtime call failed (cudaGetLastError text via cwrnnt_last_error) */
+} cwrnnt_status;
+
+/* Option bits of cwrnnt_problem.flags */
+#define CWRNNT_FUSED_LOG_SOFTMAX 0x01 /* x holds raw logits: normalise each row over V inside the op and return dense
+                                         gradients w.r.t. the logits. Clear: x holds log-probabilities (the reference
+                                         contract) and gradients are zero except the blank and label columns. */
+#define CWRNNT_COSTS_ONLY        0x02 /* backward variables only, no state for a backward pass (reference
+                                         cwarp_cuda_cal_costs, cwarp_cuda_rnnt_kernel.cu:523-576) */
+#define CWRNNT_REDUCE_MEAN       0x04 /* *loss = sum(costs) / mean_denominator; backward scales by the same factor */
+#define CWRNNT_REDUCE_SUM        0x08 /* *loss = sum(costs) */
+#define CWRNNT_AVERAGE_FRAMES    0x10 /* costs[n] (and its gradient weight) divided by T_n */
+
+#define CWRNNT_MAX_COLUMNS 4096       /* largest supported max_u + 1 */
+
+/* Bits of the device status word 0 (see cwrnnt_read_status) */
+#define CWRNNT_ST_BAD_LENGTH   0x01 /* some lx[n] < 1, ly[n] < 0 or ly[n] > max_u: nothing was computed, costs = NaN */
+#define CWRNNT_ST_ROW_MISMATCH 0x02 /* sum T_n*(U_n+1) != n_rows: nothing was computed, costs = NaN              */
+#define CWRNNT_ST_BAD_LABEL    0x04 /* a label outside [0,V) was read; it was clamped into range                   */
+#define CWRNNT_ST_FWD_BWD_GAP  0x08 /* alpha-end and beta-start differ by more than 1e-3 relative for some sequence;
+                                       as in the reference (cwarp_cuda_rnnt_kernel.cu:356-364) their mean was used */
+#define CWRNNT_ST_FATAL (CWRNNT_ST_BAD_LENGTH | CWRNNT_ST_ROW_MISMATCH)
+
+typedef struct {
+    int64_t n_rows;           /* rows of x: must equal sum_n lx[n]*(ly[n]+1) (checked on the device)      */
+    int32_t V;                /* vocabulary size = columns of x                                           */
+    int32_t B;                /* number of sequences                                                      */
+    int32_t y_stride;         /* row stride (elements) of the padded label matrix, >= max_u               */
+    int32_t max_u;            /* upper bound of ly[n]; the reference uses y.size(1) (cwarp_rnnt/__init__.py:49) */
+    int32_t blank;            /* blank index, 0 <= blank < V (cwarp_rnnt/__init__.py:50)                  */
+    int32_t dtype;            /* cwrnnt_dtype                                                             */
+    int32_t flags;            /* CWRNNT_* option bits                                                     */
+    int32_t mean_denominator; /* divisor of CWRNNT_REDUCE_MEAN; 0 means B. Sharded runs pass the global B. */
+} cwrnnt_problem;
+
+/* Library identity; replaces nothing in the reference (which exports no version from its extension). */
+CWRNNT_API int cwrnnt_abi_version(void);
+
+/* Text of a cwrnnt_status, and the CUDA error text recorded by the last CWRNNT_ERR_LAUNCH on this thread. */
+CWRNNT_API const char *cwrnnt_status_string(int status);
+CWRNNT_API const char *cwrnnt_last_error(void);
+
+/*
+ * Bytes of device workspace cwrnnt_forward needs for this problem (depends on n_rows and B only); < 0 on bad
+ * arguments. Replaces the reference's internal allocations: alphas/betas [N,Tmax,Umax+1], grads, costs, locks
+ * (cwarp_cuda_rnnt_kernel.cu:399-404), the gathered [STU,2] matrix (cwarp_cuda_gather_kernel.cu:87) and the offset
+ * tensors (cwarp_cuda.cpp:98-103). The workspace must be 256-byte aligned. It carries the state that
+ * cwrnnt_backward, cwrnnt_pair_grads and cwrnnt_export_alpha_beta read, so keep it until those have run.
+ */
+CWRNNT_API int64_t cwrnnt_workspace_bytes(const cwrnnt_problem *p);
+
+/*
+ * Forward: costs[n] = -log P(y_n | x_n), optionally the reduced loss.
+ * Replaces compact_rnnt_loss_forward (cwarp_cuda.cpp:84-108 = gather_cuda_forward + cwarp_cuda_costs_with_grad)
+ * and, with CWRNNT_COSTS_ONLY, compact_rnnt_loss (cwarp_cuda.cpp:58-82). With CWRNNT_FUSED_LOG_SOFTMAX it also
+ * replaces the caller's log_softmax (test/test.py:19-20).
+ *   x      [n_rows, V] logits or log-probs in p->dtype (row start must be 16-byte aligned for the vector path;
+ *          other shapes take a scalar path)
+ *   lx, ly [B] int32;  y [B, y_stride] int32
+ *   costs  [B] float (double for CWRNNT_F64), written
+ *   loss   1 element of the costs type or NULL; written when a CWRNNT_REDUCE_* flag is set
+ */
+CWRNNT_API int cwrnnt_forward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                   void *workspace, int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream);
+
+/*
+ * Backward: grad_x[r][k] = d (sum_n g_n * costs[n]) / d x[r][k] in one streaming pass over [n_rows, V].
+ * Replaces compact_rnnt_loss_backward_ (cwarp_cuda.cpp:110-136 = cwarp_cuda_backward_ + zeros[STU,V] +
+ * gather_cuda_backward_) and, with CWRNNT_FUSED_LOG_SOFTMAX, the caller's log_softmax backward as well.
+ *   workspace          as left by cwrnnt_forward on the same problem (not modified)
+ *   grad_costs         costs type; element n*grad_costs_stride is g_n (stride 0 broadcasts one scalar, e.g. the
+ *                      gradient of the reduced loss; the CWRNNT_REDUCE_MEAN / AVERAGE_FRAMES factors are applied
+ *                      inside). NULL means g_n = 1.
+ *   grad_x             [n_rows, V] in p->dtype, fully written (no pre-zeroing needed)
+ * Unlike the reference (cwarp_cuda_rnnt_kernel.cu:518-520) nothing saved by the forward is modified, so the call can
+ * be repeated. When a label equals `blank` the two terms add (the reference scatter overwrites one of them,
+ * cwarp_cuda_gather_kernel.cu:70-73).
+ */
+CWRNNT_API int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                    const void *workspace, const void *grad_costs, int32_t grad_costs_stride, void *grad_x,
+                    cwrnnt_stream_t stream);
+
+/*
+ * The reference's intermediate results in the reference's own shapes, for callers of its extension module
+ * (cwarp_cuda.cpp:140-143 returns (costs, grads[STU,2], alphas[N,Tmax,Umax+1], betas[N,Tmax,Umax+1])).
+ * cwrnnt_pair_grads: grads[r] = (d cost/d lp_blank, d cost/d lp_label) = (-occupancy) as in
+ * cwarp_cuda_rnnt_kernel.cu:296-307 and :325-331; costs type, [n_rows, 2], fully written.
+ * cwrnnt_export_alpha_beta: zero-padded [B, t_max, u_max1] arrays of the costs type (cwarp_cuda_rnnt_kernel.cu:399-400);
+ * either pointer may be NULL.
+ */
+CWRNNT_API int cwrnnt_pair_grads(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                      const void *workspace, void *grads, cwrnnt_stream_t stream);
+CWRNNT_API int cwrnnt_export_alpha_beta(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const void *workspace,
+                             int32_t t_max, int32_t u_max1, void *alphas, void *betas, cwrnnt_stream_t stream);
+
+/*
+ * Reference-shaped backward from saved pair gradients: dense[r][blank] = grads[r][0]*g_n, dense[r][y] =
+ * grads[r][1]*g_n, zero elsewhere. Replaces cwarp_cuda_backward_ + torch::zeros + gather_cuda_backward_
+ * (cwarp_cuda_rnnt_kernel.cu:512-521, cwarp_cuda.cpp:131-135, cwarp_cuda_gather_kernel.cu:52-74) without mutating
+ * `grads`. `scratch` needs cwrnnt_scatter_scratch_bytes(B) bytes (offsets are recomputed as cwarp_cuda.cpp:124-129).
+ * p->dtype is the type of grads, grad_costs and dense (CWRNNT_F32 or CWRNNT_F64).
+ */
+CWRNNT_API int64_t cwrnnt_scatter_scratch_bytes(int32_t B);
+CWRNNT_API int cwrnnt_scatter_backward(const cwrnnt_problem *p, const void *grads, const void *grad_costs, const int32_t *lx,
+                            const int32_t *ly, const int32_t *y, void *scratch, int64_t scratch_bytes, void *dense,
+                            cwrnnt_stream_t stream);
+
+/*
+ * Copies the 4 int32 status words of a workspace to HOST memory `out` and waits for the stream (the one call here
+ * that synchronises). out[0] = CWRNNT_ST_* bits, out[1] = first offending sequence (-1 if none), out[2] = computed
+ * sum of T_n*(U_n+1) (low 31 bits), out[3] = reserved. Replaces the reference's device printf warning
+ * (cwarp_cuda_rnnt_kernel.cu:361) and adds the checks it lacks.
+ */
+CWRNNT_API int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream);
+
+/*
+ * Host-buffer pipeline: logits, lengths and labels in HOST memory (pinned for overlap), costs / loss / gradients
+ * back in HOST memory. Sequences are cut into chunks; upload, kernels and download of successive chunks overlap on
+ * three streams. This is the call to bind where the caller's tensors live on the host. It owns its device buffers
+ * inside an opaque context (created once per device; capacity grows on demand), synchronises before returning, and
+ * is not thread-safe per context. No counterpart in the reference, which accepts CUDA tensors only
+ * (cwarp_cuda.cpp:46-52).
+ *   grad_x_host may be NULL (costs only). grad_costs_host: HOST array as in cwrnnt_backward or NULL.
+ *   chunk_rows: target rows per chunk (0 = default).
+ */
+typedef struct cwrnnt_host_ctx cwrnnt_host_ctx;
+CWRNNT_API int cwrnnt_host_ctx_create(cwrnnt_host_ctx **ctx);
+CWRNNT_API void cwrnnt_host_ctx_destroy(cwrnnt_host_ctx *ctx);
+CWRNNT_API const char *cwrnnt_host_ctx_error(const cwrnnt_host_ctx *ctx); /* CUDA error text of the last failing call */
+CWRNNT_API int cwrnnt_loss_grad_host(cwrnnt_host_ctx *ctx, const cwrnnt_problem *p, const void *x_host, const int32_t *lx_host,
+                          const int32_t *ly_host, const int32_t *y_host, const void *grad_costs_host,
+                          int32_t grad_costs_stride, void *costs_host, void *loss_host, void *grad_x_host,
+                          int64_t chunk_rows, int32_t status_out[4]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CWARP_RNNT_B200_H */

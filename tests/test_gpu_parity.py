@@ -1,0 +1,239 @@
+"""GPU parity: the CUDA engine, called through the C ABI, against the CPU oracle on the same seeded inputs.
+
+Tolerances (float32 logits): |dloss|/loss <= 1e-5 and max|dgrad| <= 1e-5, the bounds stated for this engine against the
+reference. Half-precision logits: costs are computed in float32 from the exactly-upcast inputs, so the same 1e-5
+relative bound holds against the oracle on the upcast inputs; gradients are rounded to the storage type on the way out,
+so they are allowed half an ulp of the storage type relative to the largest gradient (2^-8 for bfloat16, 2^-11 for
+float16) on top of 1e-5.
+"""
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import ragged_case
+
+pytestmark = pytest.mark.gpu
+
+LOSS_RTOL = 1e-5
+GRAD_ATOL = 1e-5
+
+
+def _upcast(case, dtype):
+    c = dict(case)
+    c["x"] = torch.as_tensor(case["x"]).to(dtype).double().numpy()
+    return c
+
+
+def _check_fused(oracle, case, dtype=torch.float32, **kw):
+    from tests.gpu_helpers import run_engine
+    got = run_engine(case, dtype=dtype, fused=True, **kw)
+    up = _upcast(case, dtype)
+    w = kw.get("grad_costs")
+    B = len(case["lx"])
+    weights = np.ones(B)
+    if w is not None:
+        weights = np.broadcast_to(np.asarray(w, dtype=np.float64), (B,)).copy()
+    scale = np.ones(B)
+    if kw.get("average_frames"):
+        scale = 1.0 / case["lx"].astype(np.float64)
+    den = kw.get("mean_denominator") or B
+    if kw.get("reduce") == "mean":
+        weights = weights / den
+    costs, dense = oracle.fused(up["x"], case["lx"], case["ly"], case["y"], case["blank"], weights=weights * scale)
+    costs = costs * scale
+    assert got["status"][0] == 0, got["status"]
+    np.testing.assert_allclose(got["costs"], costs, rtol=LOSS_RTOL, atol=1e-6)
+    if kw.get("reduce") == "mean":
+        assert abs(got["loss"] - costs.sum() / den) <= LOSS_RTOL * abs(costs.sum() / den) + 1e-6
+    if kw.get("reduce") == "sum":
+        assert abs(got["loss"] - costs.sum()) <= LOSS_RTOL * abs(costs.sum()) + 1e-6
+    atol = GRAD_ATOL
+    if dtype == torch.bfloat16:
+        atol += 2.0 ** -8 * np.abs(dense).max()
+    if dtype == torch.float16:
+        atol += 2.0 ** -11 * np.abs(dense).max()
+    err = np.abs(got["grad"] - dense).max()
+    assert err <= atol, (err, atol)
+    return got, costs, dense
+
+
+@pytest.mark.parametrize("V", [3, 5, 8, 32, 64, 100, 128, 257, 512, 1024, 2048, 4100])
+def test_fused_float32_vocab_sizes(oracle, V):
+    case = ragged_case(V, 5, (1, 23), (0, 9), V=V, sigma=2.0)
+    _check_fused(oracle, case, grad_costs=np.linspace(0.5, 1.5, 5))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float64])
+@pytest.mark.parametrize("V", [6, 64, 128, 1024, 4096])
+def test_fused_other_dtypes(oracle, dtype, V):
+    case = ragged_case(1000 + V, 4, (2, 17), (0, 8), V=V, sigma=1.5)
+    _check_fused(oracle, case, dtype=dtype)
+
+
+@pytest.mark.parametrize("reduce,avg", [("mean", False), ("sum", False), ("mean", True), (None, True)])
+def test_reductions_and_average_frames(oracle, reduce, avg):
+    case = ragged_case(77, 6, (3, 30), (1, 12), V=64)
+    _check_fused(oracle, case, reduce=reduce, average_frames=avg, grad_costs=1.7 if reduce else None)
+    _check_fused(oracle, case, reduce=reduce, average_frames=avg, mean_denominator=24 if reduce == "mean" else 0)
+
+
+def test_edge_shapes(oracle):
+    # U = 0 for every sequence (the reference cannot launch this: zero-sized grid), T = 1, single cell, blank != 0,
+    # a label equal to blank
+    c = ragged_case(5, 4, (1, 9), (0, 0), V=16)
+    _check_fused(oracle, c)
+    c = ragged_case(6, 3, (1, 1), (0, 7), V=16)
+    _check_fused(oracle, c)
+    c = ragged_case(7, 1, (1, 1), (0, 0), V=4)
+    _check_fused(oracle, c)
+    c = ragged_case(8, 4, (2, 11), (1, 6), V=24, blank=23)
+    _check_fused(oracle, c)
+    c = ragged_case(9, 4, (2, 11), (1, 6), V=12, blank=3, allow_blank_label=True)
+    c["y"][:, 0] = 3
+    _check_fused(oracle, c)
+
+
+@pytest.mark.parametrize("T,U", [(40, 31), (33, 32), (5, 200), (300, 70), (64, 1030), (20, 2100)])
+def test_wide_and_long_lattices(oracle, T, U):
+    """Column counts that cross warp seams (32), CTA width (1024 -> 2 columns per thread) and 2048 (4 per thread)."""
+    case = ragged_case(T * 7 + U, 2, (T - 3, T), (U - 2, U), V=8, sigma=1.0)
+    _check_fused(oracle, case)
+
+
+def test_many_sequences_order_and_cursor(oracle):
+    case = ragged_case(31, 300, (1, 12), (0, 6), V=8)
+    _check_fused(oracle, case, reduce="mean")
+
+
+def test_costs_only_matches_full(oracle):
+    from tests.gpu_helpers import run_engine
+    case = ragged_case(12, 7, (2, 40), (0, 25), V=48)
+    full = run_engine(case, want_grad=False)
+    only = run_engine(case, costs_only=True)
+    np.testing.assert_allclose(only["costs"], full["costs"], rtol=1e-7)
+    costs, _ = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, want_grad=False)
+    np.testing.assert_allclose(only["costs"], costs, rtol=LOSS_RTOL)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
+def test_log_prob_mode_is_reference_contract(oracle, dtype):
+    """x = log-probs: costs, sparse dense-shaped gradient, pair gradients and padded alpha/beta as the reference."""
+    from compactwarprnntloss_b200 import capi
+    from tests.gpu_helpers import run_engine
+    case = ragged_case(21, 5, (2, 21), (1, 9), V=10, sigma=1.3)
+    lp = oracle.log_softmax(case["x"])
+    c2 = dict(case, x=lp)
+    gc = np.array([1.0, 0.5, -2.0, 3.0, 0.25])
+    got = run_engine(c2, dtype=dtype, fused=False, grad_costs=gc, keep=True)
+    g = oracle.gather(torch.as_tensor(lp).to(dtype).double().numpy(), case["lx"], case["ly"], case["y"], 0)
+    fw = oracle.forward(g, case["lx"], case["ly"], want_ab=True)
+    np.testing.assert_allclose(got["costs"], fw["costs"], rtol=LOSS_RTOL)
+    dense = oracle.backward(fw["grads"], gc, case["lx"], case["ly"], case["y"], 0, 10, accumulate_equal=True)
+    assert np.abs(got["grad"] - dense).max() <= 3 * GRAD_ATOL  # |g_n| up to 3
+    # pair gradients [STU,2]
+    ct = capi.cost_dtype(dtype)
+    pg = torch.empty(lp.shape[0], 2, dtype=ct, device="cuda:0")
+    capi.pair_grads(got["p"], got["x"], got["lx"], got["ly"], got["y"], got["ws"], pg)
+    assert np.abs(pg.double().cpu().numpy() - fw["grads"]).max() <= GRAD_ATOL
+    # padded alphas / betas [N, Tmax, Umax+1]
+    Tm, Up = int(case["lx"].max()), int(case["ly"].max()) + 1
+    al = torch.full((5, Tm, Up), 7.0, dtype=ct, device="cuda:0")
+    be = torch.full((5, Tm, Up), 7.0, dtype=ct, device="cuda:0")
+    capi.export_alpha_beta(got["p"], got["lx"], got["ly"], got["ws"], Tm, Up, al, be)
+    al, be = al.double().cpu().numpy(), be.double().cpu().numpy()
+    for n in range(5):
+        T, m = int(case["lx"][n]), int(case["ly"][n]) + 1
+        o = fw["offset"][n]
+        np.testing.assert_allclose(al[n, :T, :m], fw["alpha"][o:o + T * m].reshape(T, m), rtol=1e-5, atol=1e-5)
+        np.testing.assert_allclose(be[n, :T, :m], fw["beta"][o:o + T * m].reshape(T, m), rtol=1e-5, atol=1e-5)
+        assert np.all(al[n, T:] == 0) and np.all(al[n, :, m:] == 0) and np.all(be[n, T:] == 0)
+    # reference-shaped backward from saved pair gradients
+    dn = torch.full((lp.shape[0], 10), 9.0, dtype=ct, device="cuda:0")
+    capi.scatter_backward(got["p"], pg, torch.as_tensor(gc).to(ct).cuda(), got["lx"], got["ly"], got["y"], dn)
+    assert np.abs(dn.double().cpu().numpy() - dense).max() <= 3 * GRAD_ATOL
+
+
+def test_status_words_flag_bad_inputs(oracle):
+    from compactwarprnntloss_b200 import capi
+    from tests.gpu_helpers import run_engine
+    case = ragged_case(41, 3, (2, 6), (1, 4), V=8)
+    bad = dict(case, lx=case["lx"].copy())
+    bad["lx"][1] += 1  # rows no longer add up
+    out = run_engine(bad, want_grad=False)
+    assert out["status"][0] & capi.ST_ROW_MISMATCH and np.all(np.isnan(out["costs"]))
+    bad = dict(case, lx=case["lx"].copy())
+    bad["lx"][2] = 0
+    out = run_engine(bad, want_grad=False)
+    assert out["status"][0] & capi.ST_BAD_LENGTH and out["status"][1] == 2
+    bad = dict(case, y=case["y"].copy())
+    bad["y"][0, 0] = 99
+    out = run_engine(bad, want_grad=False)
+    assert out["status"][0] == capi.ST_BAD_LABEL and np.all(np.isfinite(out["costs"]))
+    # argument errors never reach the device
+    x = torch.zeros(4, 8, device="cuda:0")
+    lx = torch.tensor([2], dtype=torch.int32, device="cuda:0")
+    y = torch.zeros(1, 1, dtype=torch.int32, device="cuda:0")
+    p = capi.make_problem(x, lx, y, blank=8, flags=0)
+    assert capi.lib().cwrnnt_workspace_bytes(p) < 0
+    p = capi.make_problem(x, lx, y, blank=0, flags=0, max_u=capi.MAX_COLUMNS)
+    p.y_stride = capi.MAX_COLUMNS
+    with pytest.raises(capi.CwrnntError):
+        capi.forward(p, x, lx, lx, y, torch.empty(1 << 20, dtype=torch.uint8, device="cuda:0"),
+                     torch.empty(1, device="cuda:0"))
+
+
+def test_backward_is_repeatable_and_linear(oracle):
+    """The saved state is never modified (the reference scales it in place): two backwards agree, and scale linearly."""
+    from tests.gpu_helpers import run_engine
+    from compactwarprnntloss_b200 import capi
+    case = ragged_case(51, 4, (3, 20), (1, 9), V=64)
+    out = run_engine(case, keep=True)
+    g1 = torch.empty_like(out["x"])
+    g2 = torch.empty_like(out["x"])
+    two = torch.tensor([2.0], device="cuda:0")
+    capi.backward(out["p"], out["x"], out["lx"], out["ly"], out["y"], out["ws"], None, 0, g1)
+    capi.backward(out["p"], out["x"], out["lx"], out["ly"], out["y"], out["ws"], two, 0, g2)
+    assert torch.equal(g1.cpu(), torch.as_tensor(out["grad"]).float())
+    assert torch.allclose(g2, 2 * g1, rtol=1e-6, atol=1e-9)
+    # rows of the logit gradient sum to zero
+    assert g1.double().sum(-1).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("cfg", [1, 2, 5])
+def test_benchmark_shapes_properties(oracle, cfg):
+    """Full-size benchmark workloads (1: tiny; 2: Conformer V=1024 fp32, subset checked against the oracle;
+    5: ragged fp16): size-independent properties plus oracle parity on the sequences the oracle finishes quickly."""
+    from compactwarprnntloss_b200 import synth
+    from tests.gpu_helpers import run_engine
+    lx, ly, y = synth.lengths_and_labels(cfg)
+    B = {1: 4, 2: 6, 5: 48}[cfg]
+    ids = list(range(B))
+    x = synth.compact_logits(cfg, lx, ly, ids)
+    case = dict(x=x.numpy() if x.dtype == torch.float32 else x, lx=lx[:B].numpy(), ly=ly[:B].numpy(),
+                y=y[:B].numpy(), blank=0, V=x.shape[1])
+    dtype = synth.WORKLOADS[cfg].dtype
+    got = run_engine(case, dtype=dtype, reduce="mean")
+    xd = x.double().numpy()
+    costs, dense = oracle.fused(xd, case["lx"], case["ly"], case["y"], 0, weights=np.full(B, 1.0 / B))
+    np.testing.assert_allclose(got["costs"], costs, rtol=LOSS_RTOL)
+    atol = GRAD_ATOL + (2.0 ** -11 * np.abs(dense).max() if dtype == torch.float16 else 0.0)
+    assert np.abs(got["grad"] - dense).max() <= atol
+    assert np.abs(got["grad"].sum(-1)).max() < (1e-4 if dtype == torch.float32 else 2e-2)
+
+
+def test_host_pipeline_matches_device_path(oracle):
+    from compactwarprnntloss_b200 import capi
+    from tests.gpu_helpers import run_engine
+    case = ragged_case(61, 9, (5, 40), (1, 12), V=128, sigma=2.0)
+    dev = run_engine(case, reduce="mean", grad_costs=0.5)
+    x = torch.as_tensor(case["x"]).pin_memory()
+    gx = torch.empty_like(x).pin_memory()
+    pipe = capi.HostPipeline(0)
+    costs, loss, st = pipe.run(x, torch.as_tensor(case["lx"]), torch.as_tensor(case["ly"]), torch.as_tensor(case["y"]),
+                               flags=capi.FUSED_LOG_SOFTMAX | capi.REDUCE_MEAN, grad_costs=torch.tensor([0.5]),
+                               grad_x=gx, chunk_rows=600)  # forces several chunks
+    pipe.close()
+    assert st[0] == 0
+    np.testing.assert_allclose(costs.numpy(), dev["costs"], rtol=1e-6)
+    assert abs(float(loss) - dev["loss"]) < 1e-5 * abs(dev["loss"])
+    assert np.abs(gx.numpy() - dev["grad"]).max() < 1e-7
