@@ -83,18 +83,21 @@ __host__ inline int64_t carve_workspace(int64_t n_rows, int32_t B, void *base, W
 // (d = t+u ascending, u ascending inside a diagonal) so that the wavefront kernel, whose thread u visits cell
 // (d-u, u) at step d, reads one contiguous, fully coalesced stream. cells_before(d) counts the cells with t+u < d:
 // inclusion-exclusion over the two box constraints t < T, u < m of the triangle count d(d+1)/2.
-__host__ __device__ inline int64_t tri(int64_t x) { return x > 0 ? x * (x + 1) / 2 : 0; }
+// (32-bit operands, one widening multiply each; a sequence has fewer than 2^31 cells.)
+__host__ __device__ inline int64_t tri(int x)
+{
+    return x > 0 ? int64_t((uint64_t(uint32_t(x)) * uint64_t(uint32_t(x) + 1u)) >> 1) : 0;
+}
 
-__host__ __device__ inline int64_t cells_before(int64_t d, int64_t T, int64_t m)
+__host__ __device__ inline int64_t cells_before(int d, int T, int m)
 {
     return tri(d) - tri(d - T) - tri(d - m) + tri(d - T - m);
 }
 
-__host__ __device__ inline int64_t diag_index(int64_t t, int64_t u, int64_t T, int64_t m)
+__host__ __device__ inline int64_t diag_index(int t, int u, int T, int m)
 {
-    int64_t d = t + u;
-    int64_t lo = d - (T - 1);
-    lo = lo > 0 ? lo : 0;
+    const int d = t + u;
+    const int lo = d - (T - 1) > 0 ? d - (T - 1) : 0;
     return cells_before(d, T, m) + (u - lo);
 }
 
@@ -200,20 +203,45 @@ struct Elt<double> {
     static __device__ __forceinline__ double from_acc(double v) { return v; }
 };
 
-// exp(v - c) for the softmax numerators. Float: one multiply and one MUFU ex2 (relative error ~2^-22); the
-// exponent-carrying subtraction is done first so the argument's rounding error scales with |v - c|, not |v|.
-__device__ __forceinline__ float exp_shifted(float v, float c) { return exp2f((v - c) * 1.4426950408889634f); }
-__device__ __forceinline__ double exp_shifted(double v, double c) { return exp(v - c); }
-
-// ln(s) for s >= 1 with an absolute error near 1e-7 even when the result is ~8: split off the binary exponent
-// (exact in double) and take logf of the mantissa in [1,2).
-__device__ __forceinline__ double log_sum(float s)
+__device__ __forceinline__ float ex2_approx(float x)
 {
-    int e;
-    float f = frexpf(s, &e);  // s = f * 2^e, f in [0.5, 1)
-    return double(e) * 0.6931471805599453 + double(logf(f));
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
-__device__ __forceinline__ double log_sum(double s) { return log(s); }
+
+// Softmax numerators exp(v - c) of one row and the matching log-sum-exp. Float: the shift is carried in base-2 units
+// (c2 = c * log2 e, rounded once), each term is one FFMA and one MUFU ex2 (relative error ~2^-22; the FFMA rounds
+// only the small difference v*log2e - c2), and the rounding of c2 is undone exactly when the row's log-sum-exp is
+// assembled in double: lse = c2 * ln 2 + ln(sum).
+template <typename A>
+struct RowShift;
+template <>
+struct RowShift<float> {
+    float c2;
+    __device__ __forceinline__ explicit RowShift(float c) : c2(c * 1.4426950408889634f) {}
+    __device__ __forceinline__ float term(float v) const { return ex2_approx(fmaf(v, 1.4426950408889634f, -c2)); }
+    // ln(s) for s >= 1 with absolute error near 1e-7 even when the result is ~8: the binary exponent is split off
+    // (exact in double) and logf sees only the mantissa in [0.5, 1).
+    __device__ __forceinline__ double lse(float s) const
+    {
+        int e;
+        const float f = frexpf(s, &e);
+        return (double(c2) + double(e)) * 0.6931471805599453 + double(logf(f));
+    }
+};
+template <>
+struct RowShift<double> {
+    double c;
+    __device__ __forceinline__ explicit RowShift(double c_) : c(c_) {}
+    __device__ __forceinline__ double term(double v) const { return exp(v - c); }
+    __device__ __forceinline__ double lse(double s) const { return c + log(s); }
+};
+
+// exp(v - c) where c is a stored log-sum-exp (gradient kernel): subtract first, so the argument's rounding error
+// scales with |v - c| and not with |v|.
+__device__ __forceinline__ float exp_shifted(float v, float c) { return ex2_approx((v - c) * 1.4426950408889634f); }
+__device__ __forceinline__ double exp_shifted(double v, double c) { return exp(v - c); }
 
 // 128-bit global loads/stores with cache hints. `nc` = read-only path; `cs` = evict-first streaming.
 __device__ __forceinline__ uint4 ld_nc(const uint4 *p) { return __ldg(p); }

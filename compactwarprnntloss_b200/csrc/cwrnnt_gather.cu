@@ -61,6 +61,7 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
             }
         }
         mx = group_max<LPR>(mx);
+        const RowShift<A> shift(mx);
         A sum = A(0);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
@@ -68,12 +69,12 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
                 A e[VE];
                 E::unpack(v[j], e);
 #pragma unroll
-                for (int c = 0; c < VE; ++c) sum += exp_shifted(e[c], mx);
+                for (int c = 0; c < VE; ++c) sum += shift.term(e[c]);
             }
         }
         sum = group_sum<LPR>(sum);
         if (live && gl == 0) {
-            const double lse = double(mx) + log_sum(sum);
+            const double lse = shift.lse(sum);
             const int64_t at = ri.off + diag_index(ri.t, ri.u, ri.T, ri.U + 1);
             w.lse[r] = lse;
             w.lp_blank[at] = double(xb) - lse;
@@ -108,11 +109,12 @@ gather_rows_generic_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B
             mx = e > mx ? e : mx;
         }
         mx = group_max<32>(mx);
+        const RowShift<A> shift(mx);
         A sum = A(0);
-        for (int k = lane; k < V; k += 32) sum += exp_shifted(E::to_acc(__ldg(row + k)), mx);
+        for (int k = lane; k < V; k += 32) sum += shift.term(E::to_acc(__ldg(row + k)));
         sum = group_sum<32>(sum);
         if (lane == 0) {
-            const double lse = double(mx) + log_sum(sum);
+            const double lse = shift.lse(sum);
             const int64_t at = ri.off + diag_index(ri.t, ri.u, ri.T, ri.U + 1);
             w.lse[r] = lse;
             w.lp_blank[at] = double(E::to_acc(__ldg(row + blank))) - lse;
