@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""fwd+bwd lattice-nodes/sec of the compact RNN-T loss on B200, with its HBM roofline and the host-CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--cfg 2]
+
+A step is one pass of the hot path over one synthetic batch: forward (row offsets, fused log-softmax + gather,
+alpha/beta wavefront, costs, loss) and backward (dense gradient w.r.t. the logits), called through the C ABI.
+
+N = 1: the Conformer-shape workload (B=32, T~U[150,250], U~U[20,80], V=1024, float32 logits), 1.3 GB of logits, larger
+than the 126 MB L2, so every step streams from HBM. N > 1 (launched by torch.distributed.run, one rank per GPU): weak
+scaling - the global batch is 32*N sequences of the same distribution, sharded by lattice size; the only collective
+is the all-reduce of the [B_global+1] cost vector.
+
+One JSON line comes out of rank 0: `value` = lattice nodes of all ranks / max-over-ranks device time with inputs
+resident in HBM; `e2e` = the same through the host-buffer entry point (pinned host logits in, host gradients out,
+PCIe copies inside the timed region); `roofline` = the gradient kernel (the dominant launch) against the measured copy
+bandwidth; `cpu_baseline` = the CPU checker (oracle/) timed on a bounded sample of the same workload.
+`--impl reference` times that CPU implementation alone (the reference project has no CPU path of its own: its three
+source files are CUDA only).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from compactwarprnntloss_b200 import synth  # noqa: E402
+
+METRIC = "fwd+bwd lattice-nodes/sec"
+UNIT = "nodes/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gradient kernel, per lattice node, from the ncu
+# capture summarised in profiles/grad_rows_kernel_conformer_v1024.md (V=1024 float32; algorithmic figure is 8192).
+GRAD_KERNEL_DRAM_BYTES_PER_NODE = {2: 8039.0}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cfg", type=int, default=2, help="workload (1-5); the headline metric is quoted on 2")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-seqs", type=int, default=8)
+    return ap.parse_args()
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled every 100 ms while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.rows, self.proc = [], None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", sel, "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self):
+        return len(self.rows)
+
+    def stop(self, start=0):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        rows = [r for r in self.rows[start:] if len(r) >= 7] or [r for r in self.rows if len(r) >= 7]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(rows[0][1]),
+                "power_w_max": max(float(r[2]) for r in rows), "samples": len(rows), "reasons": reasons}
+
+
+def cpu_reference_time(cfg, lx, ly, y, n_seqs, reps):
+    """The CPU checker's fused float32 pipeline (all host threads) on the first n_seqs sequences; nodes/s."""
+    from oracle import oracle
+    oracle.build()
+    import numpy as np
+    ids = list(range(min(n_seqs, len(lx))))
+    x = synth.compact_logits(cfg, lx, ly, ids).float().numpy()
+    lxs, lys, ys = lx[ids].numpy(), ly[ids].numpy(), y[ids].numpy()
+    out = np.empty_like(x)
+    w = np.full(len(ids), 1.0 / len(lx))
+    oracle.fused_f32io(x[: int(lxs[0]) * (int(lys[0]) + 1)], lxs[:1], lys[:1], ys[:1], 0)  # touch the library
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        oracle.fused_f32io(x, lxs, lys, ys, 0, weights=w, dense_out=out)
+        times.append(time.perf_counter() - t0)
+    nodes = x.shape[0]
+    return nodes / min(times), oracle.num_threads(), nodes, sum(times)
+
+
+def run_reference(args):
+    """--impl reference: the path's CPU implementation on the box's host cores. The reference project itself is CUDA
+    only, so this is the CPU checker (oracle/rnnt_oracle.c, OpenMP over rows and sequences)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = args.cfg
+    lx, ly, y = synth.lengths_and_labels(cfg)
+    n_seqs = args.cpu_sample_seqs
+    from oracle import oracle
+    oracle.build()
+    import numpy as np
+    ids = list(range(min(n_seqs, len(lx))))
+    x = synth.compact_logits(cfg, lx, ly, ids).float().numpy()
+    lxs, lys, ys = lx[ids].numpy(), ly[ids].numpy(), y[ids].numpy()
+    out = np.empty_like(x)
+    w = np.full(len(ids), 1.0 / len(lx))
+    for _ in range(max(args.warmup, 1)):
+        oracle.fused_f32io(x[: int(lxs[0]) * (int(lys[0]) + 1)], lxs[:1], lys[:1], ys[:1], 0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.fused_f32io(x, lxs, lys, ys, 0, weights=w, dense_out=out)
+    dt = time.perf_counter() - t0
+    nodes = x.shape[0]
+    value = nodes * args.steps / dt
+    wl = synth.WORKLOADS[cfg]
+    sample = f"first {len(ids)} of {wl.B} sequences of the workload ({nodes} lattice nodes) per step"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.name, "sample": sample, "host_threads": oracle.num_threads()},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    from compactwarprnntloss_b200 import capi, sharding
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback of the product path)")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = args.cfg
+    wl = synth.WORKLOADS[cfg]
+
+    # ---- workload: weak scaling, B = wl.B * world sequences sharded by lattice size
+    B_global = wl.B * world
+    lx, ly, y = synth.lengths_and_labels(cfg, B=B_global)
+    plan = sharding.plan_shards(lx.tolist(), ly.tolist(), world)
+    sharding.validate_plan(plan, B_global)
+    ids = plan[rank]
+    x_host = synth.compact_logits(cfg, lx, ly, ids, pin=True)
+    lx_l, ly_l, y_l = lx[ids].contiguous(), ly[ids].contiguous(), y[ids].contiguous()
+    nodes_local = x_host.shape[0]
+    nodes_global = synth.lattice_nodes(lx, ly)
+    elt = x_host.element_size()
+
+    x = x_host.to(dev)
+    lxd, lyd, yd = lx_l.to(dev), ly_l.to(dev), y_l.to(dev)
+    flags = capi.FUSED_LOG_SOFTMAX | (capi.REDUCE_MEAN if wl.reduction == "mean" else capi.REDUCE_SUM)
+    p = capi.make_problem(x, lxd, yd, 0, flags, mean_denominator=B_global)
+    ws = capi.alloc_workspace(p, dev)
+    ct = capi.cost_dtype(x.dtype)
+    costs = torch.empty(p.B, dtype=ct, device=dev)
+    loss = torch.zeros((), dtype=ct, device=dev)
+    gx = torch.empty_like(x)
+    one = torch.ones(1, dtype=ct, device=dev)
+    vec = torch.empty(B_global + 1, dtype=ct, device=dev)
+
+    def step():
+        capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
+        if world > 1:
+            sharding.exchange_costs(costs, ids, B_global, local_loss=loss, out=vec)
+        capi.backward(p, x, lxd, lyd, yd, ws, one, 0, gx)
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    fence()
+    st = capi.read_status(ws)
+    if st[0] & 0x3:
+        raise SystemExit(f"device status reports invalid inputs: {st}")
+
+    # ---- timed region: CUDA events on the launching stream, per-step marks for the kernel breakdown
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local) if rank == 0 else None
+    fence()
+    mark = sampler.mark() if sampler else 0
+    for k in range(K):
+        ev[k][0].record()
+        capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
+        if world > 1:
+            sharding.exchange_costs(costs, ids, B_global, local_loss=loss, out=vec)
+        ev[k][1].record()
+        capi.backward(p, x, lxd, lyd, yd, ws, one, 0, gx)
+        ev[k][2].record()
+    end = torch.cuda.Event(enable_timing=True)
+    end.record()
+    fence()
+    clocks = sampler.stop(mark) if sampler else None
+    total_ms = ev[0][0].elapsed_time(end)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+    t = torch.tensor([total_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms = [float(v) for v in t.cpu()]
+    ms_per_step = total_ms / K
+    value = nodes_global / (ms_per_step * 1e-3)
+    loss_value = float(vec[B_global] if world > 1 else loss)
+
+    # ---- end to end through the host-buffer entry point: pinned host logits in, host gradients + costs out
+    e2e = None
+    if not args.no_e2e:
+        pipe = capi.HostPipeline(dev)
+        g_host = torch.empty_like(x_host).pin_memory()
+        gc = torch.ones(1, dtype=ct)
+        e2e_steps = max(2, min(K, 5))
+
+        def e2e_step():
+            c, l, s = pipe.run(x_host, lx_l, ly_l, y_l, blank=0, flags=flags, grad_costs=gc, grad_x=g_host,
+                               mean_denominator=B_global)
+            if world > 1:
+                sharding.exchange_costs(c.to(dev), ids, B_global, local_loss=l.to(dev), out=vec)
+                vec.cpu()
+            return l
+
+        e2e_step()
+        fence()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            l_host = e2e_step()
+        fence()
+        dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        e2e_s = float(dt.cpu()) / e2e_steps
+        small = (lx_l.numel() * 2 + y_l.numel()) * 4
+        e2e = {"value": nodes_global / e2e_s, "unit": UNIT,
+               "h2d_bytes_per_step": int(x_host.numel() * elt + small + 4),
+               "d2h_bytes_per_step": int(g_host.numel() * elt + p.B * 4 + 16),
+               "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
+               "what": "cwrnnt_loss_grad_host: pinned host logits -> device (chunked, 3 streams) -> host gradients "
+                       "and costs; per-rank bytes",
+               "loss": float(l_host)}
+        pipe.close()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peak()
+    grad_bytes = 2.0 * nodes_local * wl.V * elt  # one launch: every row read once and written once
+    achieved = grad_bytes / (bwd_ms * 1e-3) / 1e9
+    traffic = GRAD_KERNEL_DRAM_BYTES_PER_NODE.get(cfg)
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[wl.dtype],
+        "data": "synthetic",
+        "config": {"workload": wl.name, "global_sequences": B_global, "lattice_nodes": nodes_global,
+                   "logits_bytes_per_gpu": int(x_host.numel() * elt), "sharding": f"lattice-size LPT over {world} rank(s)",
+                   "l2": "inputs larger than L2 (no flush needed)", "reduction": wl.reduction,
+                   "shard_imbalance": round(sharding.shard_imbalance(lx, ly, plan), 4)},
+        "gpu_launches": 4 * K,
+        "kernels_per_step": ["prep_kernel", "gather_rows_kernel", "wavefront_kernel", "grad_rows_kernel"],
+        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "loss": loss_value,
+        "roofline": {"bound": "hbm", "kernel": "grad_rows_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                     "traffic": traffic * nodes_local if traffic else None,
+                     "algorithmic_bytes": grad_bytes, "launch_ms": bwd_ms},
+        "step_roofline": {"achieved": 3.0 * nodes_local * wl.V * elt / (ms_per_step * 1e-3) / 1e9, "peak": peak,
+                          "unit": "GB/s", "frac": 3.0 * nodes_local * wl.V * elt / (ms_per_step * 1e-3) / 1e9 / peak,
+                          "bytes_per_node": 3 * wl.V * elt},
+        "clocks": clocks,
+    }
+    if e2e:
+        out["e2e"] = e2e
+    if world == 1 and not args.no_cpu_baseline:
+        v, cores, nodes, spent = cpu_reference_time(cfg, lx, ly, y, args.cpu_sample_seqs, reps=3)
+        out["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                               "sample": f"first {min(args.cpu_sample_seqs, wl.B)} of {wl.B} sequences ({nodes} "
+                                         f"lattice nodes), best of 3, {spent:.1f} s of CPU wall time"}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
