@@ -1,0 +1,129 @@
+"""`transducer_loss`: the reference's Python entry point (cwarp_rnnt/__init__.py:32-73) on the B200 engine.
+
+Same positional signature and argument contract; keyword-only additions:
+
+gather              accepted for callers that pass ``gather=True`` to comparable packages; the compact engine always
+                    gathers the blank and label columns internally, so both values give the same result.
+average_frames      divide each sequence's cost (and its gradient) by its frame count T_n before the reduction.
+fused_log_softmax   False (default, the reference contract): ``x`` holds log-probabilities and the gradient is zero
+                    except at the blank and label columns. True: ``x`` holds raw logits; the row-wise log-softmax and
+                    its backward are fused into the loss kernels and the gradient is dense. On already-normalised
+                    input both settings return the same loss.
+check               True (default): the reference's assertions, including the one that reads ``ly.max()`` on the host,
+                    plus a read of the device status word after the forward (one synchronisation). False: no host
+                    synchronisation at all; invalid lengths then surface as NaN costs.
+
+The CUDA extension is mandatory: importing this module without it raises ImportError (no CPU or PyTorch fallback).
+"""
+from typing import Any, Literal, Optional
+
+import torch
+
+try:
+    from . import _C as core
+except ImportError as e:  # pragma: no cover - exercised only on a box without the built extension
+    raise ImportError("compactwarprnntloss_b200._C is not built; run `python -m compactwarprnntloss_b200.build` "
+                      "(the package has no CPU or PyTorch fallback)") from e
+
+__all__ = ["transducer_loss", "TransducerLoss", "compact_from_padded"]
+
+
+class _TransLoss(torch.autograd.Function):
+    """forward -> (costs [N], loss []); only one of the two is consumed, depending on the reduction."""
+
+    @staticmethod
+    def forward(ctx: Any, xs, lx, ys, ly, blank, flags, mean_denominator, check):
+        needs_grad = xs.requires_grad
+        run_flags = flags if needs_grad else (flags | core.COSTS_ONLY)
+        costs, loss, ws = core._rnnt_forward(xs, lx, ys, ly, blank, run_flags, mean_denominator)
+        if check:
+            st = core._rnnt_status(ws)
+            if st[0] & core.ST_BAD_LENGTH:
+                raise ValueError(f"invalid length at sequence {st[1]}: need lx >= 1 and 0 <= ly <= y.size(1)")
+            if st[0] & core.ST_ROW_MISMATCH:
+                raise ValueError(f"x has {xs.size(0)} rows but sum(lx*(ly+1)) is different")
+            if st[0] & core.ST_BAD_LABEL:
+                raise ValueError("a label lies outside [0, V)")
+        if needs_grad:
+            ctx.save_for_backward(xs, lx, ys, ly, ws)
+            ctx.blank, ctx.flags, ctx.mean_denominator = blank, flags, mean_denominator
+        ctx.mark_non_differentiable(*(() if needs_grad else (costs, loss)))
+        return costs, loss
+
+    @staticmethod
+    def backward(ctx: Any, grad_costs, grad_loss):
+        xs, lx, ys, ly, ws = ctx.saved_tensors
+        reduced = ctx.flags & (core.REDUCE_MEAN | core.REDUCE_SUM)
+        g = grad_loss if reduced else grad_costs
+        grad_x = core._rnnt_backward(xs, lx, ys, ly, ctx.blank, ctx.flags, ctx.mean_denominator, ws,
+                                     g.contiguous())
+        return grad_x, None, None, None, None, None, None, None
+
+
+def compact_from_padded(x: torch.Tensor, lx: torch.Tensor, ly: torch.Tensor) -> torch.Tensor:
+    """[N, T, U+1, V] padded joint output -> compact [sum_i T_i*(U_i+1), V], keeping x[i, :T_i, :U_i+1] of every
+    sequence in (t, u) row-major order (the layout of the reference's test/test.py:34-48). Differentiable."""
+    N, T, Up, V = x.shape
+    t_ok = torch.arange(T, device=x.device)[None, :] < lx[:, None].to(x.device)
+    u_ok = torch.arange(Up, device=x.device)[None, :] <= ly[:, None].to(x.device)
+    mask = t_ok[:, :, None] & u_ok[:, None, :]
+    return x[mask]
+
+
+def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torch.Tensor, blank: int = 0,
+                    reduction: Optional[Literal["mean", "sum", "none"]] = "mean", *, gather: bool = True,
+                    average_frames: bool = False, fused_log_softmax: bool = False, check: bool = True,
+                    mean_denominator: int = 0) -> torch.Tensor:
+    """Transducer loss with compact layout. See the module docstring for the keyword-only options."""
+    del gather  # always on
+    assert lx.dtype == torch.int32
+    assert ly.dtype == torch.int32
+    assert y.dtype == torch.int32
+    assert reduction in ["mean", "sum", "none"] or reduction is None
+    # y: (N, U)
+    assert y.dim() == 2
+    assert y.size(0) == lx.size(0)
+    assert y.size(0) == ly.size(0)
+    if check:
+        assert y.size(1) == ly.max()
+    assert blank >= 0 and blank < x.size(-1)
+
+    if x.dim() == 4:
+        print("WARNING: it seems your input is not compact... would try to compact the input.")
+        N, T, Up, V = x.size()
+        assert y.size(1) + 1 == Up
+        if check:
+            assert lx.max() == T
+        x = compact_from_padded(x, lx, ly)
+
+    # x: (STU, V)
+    assert x.dim() == 2
+
+    flags = 0
+    if fused_log_softmax:
+        flags |= core.FUSED_LOG_SOFTMAX
+    if average_frames:
+        flags |= core.AVERAGE_FRAMES
+    if reduction == "mean":
+        flags |= core.REDUCE_MEAN
+    elif reduction == "sum":
+        flags |= core.REDUCE_SUM
+    elif not (reduction == "none" or reduction is None):
+        raise ValueError
+
+    costs, loss = _TransLoss.apply(x.contiguous(), lx, y.contiguous(), ly, blank, flags, mean_denominator, check)
+    return loss if reduction in ("mean", "sum") else costs
+
+
+class TransducerLoss(torch.nn.Module):
+    """Module form of :func:`transducer_loss`."""
+
+    def __init__(self, blank: int = 0, reduction: Optional[str] = "mean", average_frames: bool = False,
+                 fused_log_softmax: bool = False, check: bool = True):
+        super().__init__()
+        self.blank, self.reduction = blank, reduction
+        self.average_frames, self.fused_log_softmax, self.check = average_frames, fused_log_softmax, check
+
+    def forward(self, x, lx, y, ly):
+        return transducer_loss(x, lx, y, ly, self.blank, self.reduction, average_frames=self.average_frames,
+                               fused_log_softmax=self.fused_log_softmax, check=self.check)

@@ -1,0 +1,191 @@
+"""GPU tests of the reference-facing Python surface: `cwarp_rnnt.transducer_loss`, the `cwarp_rnnt._C` functions with
+the reference's shapes, autograd, and - when oracle/_ref was built - the reference's own CUDA kernels run live on the
+same inputs.
+
+Bounds against the reference are triangle bounds: the reference computes alpha/beta in float32, and its own distance
+to the double-precision truth grows with lattice size (4e-6 at 40 diagonals, 9e-4 at 330, see tests/test_golden.py);
+this engine stays within 1e-5 of the truth, so |ours - ref| <= |ref - truth| + 1e-5.
+"""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.helpers import ragged_case
+
+pytestmark = pytest.mark.gpu
+GOLD = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "ref_*.npz")))
+DEV = "cuda:0"
+
+
+def _tensors(case, dtype=torch.float32, x=None):
+    x = torch.as_tensor(case["x"] if x is None else x).to(dtype).to(DEV)
+    return (x, torch.as_tensor(case["lx"]).to(DEV), torch.as_tensor(case["y"]).to(DEV).contiguous(),
+            torch.as_tensor(case["ly"]).to(DEV))
+
+
+@pytest.mark.parametrize("reduction", ["mean", "sum", "none", None])
+def test_drop_in_log_prob_contract(oracle, reduction):
+    import cwarp_rnnt
+    case = ragged_case(3, 5, (2, 25), (1, 10), V=12, sigma=1.5)
+    lp = oracle.log_softmax(case["x"]).astype(np.float32)
+    x, lx, y, ly = _tensors(case, x=lp)
+    x.requires_grad_(True)
+    out = cwarp_rnnt.transducer_loss(x, lx, y, ly, 0, reduction)
+    g = oracle.gather(lp.astype(np.float64), case["lx"], case["ly"], case["y"], 0)
+    fw = oracle.forward(g, case["lx"], case["ly"])
+    if reduction in ("none", None):
+        assert out.shape == (5,)
+        np.testing.assert_allclose(out.detach().cpu().numpy(), fw["costs"], rtol=1e-5)
+        w = torch.linspace(0.5, 2.0, 5, device=DEV)
+        (out * w).sum().backward()
+        weights = w.cpu().numpy().astype(np.float64)
+    else:
+        want = fw["costs"].mean() if reduction == "mean" else fw["costs"].sum()
+        assert out.dim() == 0 and abs(float(out) - want) <= 1e-5 * abs(want)
+        out.backward()
+        weights = np.full(5, 1.0 / 5 if reduction == "mean" else 1.0)
+    dense = oracle.backward(fw["grads"], weights, case["lx"], case["ly"], case["y"], 0, 12, accumulate_equal=True)
+    assert np.abs(x.grad.cpu().numpy() - dense).max() <= 2e-5
+
+
+def test_fused_equals_log_softmax_then_loss(oracle):
+    """fused_log_softmax=True on logits == torch.log_softmax followed by the log-prob contract, loss and gradient."""
+    import cwarp_rnnt
+    case = ragged_case(8, 4, (3, 30), (0, 12), V=40, sigma=2.0)
+    x, lx, y, ly = _tensors(case)
+    a = x.clone().requires_grad_(True)
+    b = x.clone().requires_grad_(True)
+    la = cwarp_rnnt.transducer_loss(a, lx, y, ly, 0, "mean", fused_log_softmax=True, average_frames=True)
+    lb = cwarp_rnnt.transducer_loss(torch.log_softmax(b, -1), lx, y, ly, 0, "mean", average_frames=True)
+    la.backward()
+    lb.backward()
+    assert abs(float(la) - float(lb)) <= 1e-5 * abs(float(lb))
+    assert (a.grad - b.grad).abs().max().item() <= 1e-5
+    w = np.full(4, 0.25) / case["lx"]
+    costs, dense = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, weights=w)
+    assert abs(float(la) - (costs / case["lx"]).mean()) <= 1e-5 * abs(float(la))
+    assert np.abs(a.grad.cpu().numpy() - dense).max() <= 1e-5
+
+
+def test_no_grad_path_and_unchecked_path(oracle):
+    import cwarp_rnnt
+    case = ragged_case(13, 6, (2, 18), (1, 9), V=16)
+    x, lx, y, ly = _tensors(case)
+    costs, _ = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, want_grad=False)
+    out = cwarp_rnnt.transducer_loss(x, lx, y, ly, 0, "none", fused_log_softmax=True)
+    assert not out.requires_grad
+    np.testing.assert_allclose(out.cpu().numpy(), costs, rtol=1e-5)
+    out2 = cwarp_rnnt.transducer_loss(x, lx, y, ly, 0, "none", fused_log_softmax=True, check=False, gather=True)
+    assert torch.equal(out, out2)
+
+
+def test_padded_4d_input_is_compacted_per_sequence(oracle, capsys):
+    import cwarp_rnnt
+    case = ragged_case(17, 3, (4, 9), (1, 5), V=7)
+    lx, ly = case["lx"], case["ly"]
+    lx[0], ly[1] = 9, 5  # maxima attained, as the entry point asserts
+    case = ragged_case(17, 3, (4, 9), (1, 5), V=7)
+    case["lx"][0], case["ly"][1] = 9, 5
+    N, T, Up, V = 3, 9, 6, 7
+    rng = np.random.default_rng(0)
+    xp = rng.standard_normal((N, T, Up, V)).astype(np.float32)
+    y = rng.integers(1, V, size=(N, Up - 1)).astype(np.int32)
+    rows = [xp[n, :case["lx"][n], :case["ly"][n] + 1].reshape(-1, V) for n in range(N)]
+    compact = np.concatenate(rows)
+    costs, _ = oracle.fused(compact, case["lx"], case["ly"], y, 0, want_grad=False)
+    x4 = torch.tensor(xp, device=DEV, requires_grad=True)
+    out = cwarp_rnnt.transducer_loss(x4, torch.tensor(case["lx"], device=DEV), torch.tensor(y, device=DEV),
+                                     torch.tensor(case["ly"], device=DEV), 0, "sum", fused_log_softmax=True)
+    assert "not compact" in capsys.readouterr().out
+    assert abs(float(out) - costs.sum()) <= 1e-5 * costs.sum()
+    out.backward()
+    g = x4.grad.cpu().numpy()
+    assert np.all(g[1, case["lx"][1]:] == 0) and np.abs(g[0, :case["lx"][0], :case["ly"][0] + 1]).max() > 0
+
+
+def test_error_behaviour_matches_reference():
+    import cwarp_rnnt
+    case = ragged_case(19, 2, (3, 6), (1, 3), V=5)
+    x, lx, y, ly = _tensors(case)
+    with pytest.raises(AssertionError):
+        cwarp_rnnt.transducer_loss(x, lx.long(), y, ly)          # lx must be int32   (reference __init__.py:41)
+    with pytest.raises(AssertionError):
+        cwarp_rnnt.transducer_loss(x, lx, y, ly, blank=5)        # blank < V          (reference __init__.py:50)
+    with pytest.raises(AssertionError):
+        cwarp_rnnt.transducer_loss(x, lx, y[:, :-1].contiguous(), ly)  # y.size(1) == ly.max()  (:49)
+    with pytest.raises(AssertionError):
+        cwarp_rnnt.transducer_loss(x, lx, y, ly, reduction="avg")
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        cwarp_rnnt.transducer_loss(x.cpu(), lx, y, ly)           # reference cwarp_cuda.cpp:46
+    with pytest.raises(ValueError, match="rows"):
+        cwarp_rnnt.transducer_loss(x[:-1].contiguous(), lx, y, ly)   # the reference would read out of bounds here
+    with pytest.raises(TypeError):
+        cwarp_rnnt.transducer_loss(x, lx, y, ly, 0, "mean", True)    # the extras are keyword-only
+
+
+def test_gradcheck_double_fused():
+    import cwarp_rnnt
+    case = ragged_case(23, 2, (2, 4), (1, 3), V=4)
+    x, lx, y, ly = _tensors(case, dtype=torch.float64)
+    x.requires_grad_(True)
+    f = lambda t: cwarp_rnnt.transducer_loss(t, lx, y, ly, 0, "none", fused_log_softmax=True, check=False)  # noqa: E731
+    assert torch.autograd.gradcheck(f, (x,), eps=1e-6, atol=1e-6, rtol=1e-5, nondet_tol=0.0)
+
+
+@pytest.mark.parametrize("path", GOLD, ids=[os.path.basename(p)[4:-4] for p in GOLD])
+def test_extension_functions_against_golden_reference_outputs(oracle, path):
+    """`cwarp_rnnt._C` with the reference's shapes on the inputs the reference itself was run on (fixtures)."""
+    import cwarp_rnnt._C as core
+    z = np.load(path)
+    if "lp" not in z.files:
+        pytest.skip("fixture stores the gathered pair only")
+    lx, ly = torch.tensor(z["lx"], device=DEV), torch.tensor(z["ly"], device=DEV)
+    y = torch.tensor(z["y"], device=DEV).contiguous()
+    lp = torch.tensor(z["lp"], device=DEV)
+    costs, grads, alphas, betas = core._cwarp_rnnt_forward(lp, lx, y, ly, 0)
+    costs_only = core._cwarp_rnnt_loss(lp, lx, y, ly, 0)
+    f64 = oracle.forward(z["g"].astype(np.float64), z["lx"], z["ly"])
+    ref_err = np.abs(z["grads"] - f64["grads"]).max()
+    assert costs.shape == z["costs"].shape and grads.shape == z["grads"].shape
+    assert alphas.shape == z["alphas"].shape and betas.shape == z["betas"].shape
+    np.testing.assert_allclose(costs.cpu().numpy(), z["costs"], rtol=1e-5)
+    np.testing.assert_allclose(costs_only.cpu().numpy(), z["costs"], rtol=1e-5)
+    assert np.abs(grads.cpu().numpy() - f64["grads"]).max() <= 1e-5
+    assert np.abs(grads.cpu().numpy() - z["grads"]).max() <= ref_err + 1e-5
+    scale = np.abs(z["costs"]).max()
+    assert np.abs(alphas.cpu().numpy() - z["alphas"]).max() <= 2e-6 * scale
+    assert np.abs(betas.cpu().numpy() - z["betas"]).max() <= 2e-6 * scale
+    saved = grads.clone()
+    dense = core._cwarp_rnnt_backward(grads, torch.tensor(z["grad_costs"], device=DEV), y, lx, ly, 0, int(z["V"]))
+    assert torch.equal(grads, saved)  # not scaled in place, unlike the reference
+    assert np.abs(dense.cpu().numpy() - z["dense"]).max() <= 2.0 * ref_err + 2e-5
+
+
+def test_live_reference_cuda_kernels_when_built(oracle):
+    """ours vs the reference's CUDA kernels (oracle/_ref, sm_100a build of its unmodified sources) on a Conformer-shape
+    lattice: loss within 1e-5 relative; gradients within the reference's own float32 error + 1e-5."""
+    from oracle.build_ref import load_ref
+    import cwarp_rnnt
+    ref = load_ref()
+    if ref is None:
+        pytest.skip("oracle/_ref not built on this machine")
+    case = ragged_case(29, 4, (150, 250), (20, 80), V=32, sigma=2.0)
+    x, lx, y, ly = _tensors(case)
+    a = x.clone().requires_grad_(True)
+    lp = torch.log_softmax(a, -1)
+    costs_r, grads_r, _, _ = ref._cwarp_rnnt_forward(lp.detach().contiguous(), lx, y, ly, 0)
+    dense_r = ref._cwarp_rnnt_backward(grads_r.clone(), torch.full((4,), 0.25, device=DEV), y, lx, ly, 0, 32)
+    lp.backward(dense_r)
+    b = x.clone().requires_grad_(True)
+    ours = cwarp_rnnt.transducer_loss(b, lx, y, ly, 0, "mean", fused_log_softmax=True)
+    ours.backward()
+    costs64, dense64 = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, weights=np.full(4, 0.25))
+    ref_err = np.abs(a.grad.cpu().numpy() - dense64).max()
+    our_err = np.abs(b.grad.cpu().numpy() - dense64).max()
+    assert abs(float(ours) - float(costs_r.mean())) <= 1e-5 * abs(float(ours))
+    assert our_err <= 1e-5
+    assert (a.grad - b.grad).abs().max().item() <= ref_err + 1e-5
+    print(f"|ours-f64| {our_err:.2e}  |ref-f64| {ref_err:.2e}  |ours-ref| {(a.grad - b.grad).abs().max().item():.2e}")
