@@ -16,6 +16,8 @@ F32, F16, BF16, F64 = 0, 1, 2, 3
 FUSED_LOG_SOFTMAX, COSTS_ONLY, REDUCE_MEAN, REDUCE_SUM, AVERAGE_FRAMES = 0x01, 0x02, 0x04, 0x08, 0x10
 ST_BAD_LENGTH, ST_ROW_MISMATCH, ST_BAD_LABEL, ST_FWD_BWD_GAP = 0x01, 0x02, 0x04, 0x08
 MAX_COLUMNS = 4096
+STATIC_MAX_ROWS, STATIC_MAX_SEQUENCES = 131072, 1024
+ERR_CAPACITY = 5
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.float64: F64}
 
@@ -23,7 +25,7 @@ EXPORTS = [
     "cwrnnt_abi_version", "cwrnnt_status_string", "cwrnnt_last_error", "cwrnnt_workspace_bytes", "cwrnnt_forward",
     "cwrnnt_backward", "cwrnnt_pair_grads", "cwrnnt_export_alpha_beta", "cwrnnt_scatter_scratch_bytes",
     "cwrnnt_scatter_backward", "cwrnnt_read_status", "cwrnnt_host_ctx_create", "cwrnnt_host_ctx_destroy",
-    "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host",
+    "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static",
 ]
 
 
@@ -62,6 +64,7 @@ def lib():
         L.cwrnnt_scatter_scratch_bytes.restype = i64
         L.cwrnnt_scatter_scratch_bytes.argtypes = [i32]
         L.cwrnnt_scatter_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i64, vp, vp]
+        L.cwrnnt_costs_static.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_read_status.argtypes = [vp, ctypes.POINTER(i32 * 4), vp]
         L.cwrnnt_host_ctx_create.argtypes = [ctypes.POINTER(vp)]
         L.cwrnnt_host_ctx_destroy.argtypes = [vp]
@@ -77,7 +80,7 @@ def check(status: int, what: str = "cwrnnt") -> None:
     if status != 0:
         L = lib()
         msg = L.cwrnnt_status_string(status).decode()
-        if status == 4:
+        if status in (4, 5):
             msg += ": " + L.cwrnnt_last_error().decode()
         raise CwrnntError(f"{what}: {msg} (status {status})")
 
@@ -152,6 +155,15 @@ def scatter_backward(p: Problem, grads, grad_costs, lx, ly, y, dense) -> None:
         check(lib().cwrnnt_scatter_backward(ctypes.byref(p), _ptr(grads), _ptr(grad_costs), _ptr(lx), _ptr(ly),
                                             _ptr(y), _ptr(scratch), n, _ptr(dense), _stream(grads.device)),
               "cwrnnt_scatter_backward")
+
+
+def costs_static(p: Problem, x, lx, ly, y, costs, loss=None) -> None:
+    """Costs-only forward on the library's built-in scratch: no workspace argument, nothing allocated. Problems above
+    STATIC_MAX_ROWS rows / STATIC_MAX_SEQUENCES sequences raise CwrnntError (status 5). Calls on one device share the
+    scratch, so keep them on one stream."""
+    with torch.cuda.device(x.device):
+        check(lib().cwrnnt_costs_static(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(costs),
+                                        _ptr(loss), _stream(x.device)), "cwrnnt_costs_static")
 
 
 def read_status(workspace: torch.Tensor):

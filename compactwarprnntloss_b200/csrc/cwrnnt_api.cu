@@ -42,6 +42,8 @@ int check_workspace(const cwrnnt_problem *p, const void *ws, int64_t bytes, Work
 
 }  // namespace
 
+void cwrnnt::set_last_error(const char *text) { std::snprintf(g_last_error, sizeof g_last_error, "%s", text); }
+
 extern "C" {
 
 int cwrnnt_abi_version(void) { return CWRNNT_ABI_VERSION; }
@@ -54,6 +56,7 @@ const char *cwrnnt_status_string(int status)
     case CWRNNT_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
     case CWRNNT_ERR_UNSUPPORTED: return "label length above the supported maximum";
     case CWRNNT_ERR_LAUNCH: return "CUDA launch or runtime failure";
+    case CWRNNT_ERR_CAPACITY: return "problem larger than the fixed capacity of this entry point";
     }
     return "unknown status";
 }

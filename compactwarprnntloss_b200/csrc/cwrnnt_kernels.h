@@ -4,6 +4,9 @@
 
 namespace cwrnnt {
 
+// Text returned by cwrnnt_last_error() on the calling thread.
+void set_last_error(const char *text);
+
 // K0: offsets, validation, longest-first order. 1 CTA.
 cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
                         void *costs, cudaStream_t s);

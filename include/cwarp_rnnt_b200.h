@@ -43,7 +43,8 @@ typedef enum {
     CWRNNT_ERR_ARGUMENT = 1,   /* null pointer, negative size, blank outside [0,V), unknown dtype or flag */
     CWRNNT_ERR_WORKSPACE = 2,  /* workspace pointer misaligned or smaller than cwrnnt_workspace_bytes()   */
     CWRNNT_ERR_UNSUPPORTED = 3,/* max_u + 1 above CWRNNT_MAX_COLUMNS                                      */
-    CWRNNT_ERR_LAUNCH = 4      /* a CUDA launch or runtime call failed (cudaGetLastError text via cwrnnt_last_error) */
+    CWRNNT_ERR_LAUNCH = 4,     /* a CUDA launch or runtime call failed (cudaGetLastError text via cwrnnt_last_error) */
+    CWRNNT_ERR_CAPACITY = 5    /* more rows or sequences than cwrnnt_costs_static holds scratch for            */
 } cwrnnt_status;
 
 /* Option bits of cwrnnt_problem.flags */
@@ -157,6 +158,29 @@ CWRNNT_API int cwrnnt_scatter_backward(const cwrnnt_problem *p, const void *grad
  * (cwarp_cuda_rnnt_kernel.cu:361) and adds the checks it lacks.
  */
 CWRNNT_API int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream);
+
+/*
+ * Costs (and the reduced loss) without any caller workspace and without any allocation: for hosts that cannot call
+ * cudaMalloc - a plug-in in a serving process whose framework owns all device memory, a foreign-language binding with
+ * no device allocator to size a workspace with, a scoring loop that cannot afford the synchronisation an allocation
+ * implies. No counterpart in the reference (which allocates five tensors per call, cwarp_cuda_rnnt_kernel.cu:535-537,
+ * cwarp_cuda_gather_kernel.cu:87). Same arguments and results as cwrnnt_forward with CWRNNT_COSTS_ONLY (the flag is
+ * implied); the scratch is a fixed device array inside the library (about 5.3 MB, held by every GPU that loads the
+ * library until the process exits), so:
+ *   - problems above CWRNNT_STATIC_MAX_ROWS rows or CWRNNT_STATIC_MAX_SEQUENCES sequences are refused with
+ *     CWRNNT_ERR_CAPACITY before anything is launched;
+ *   - the first call on each device resolves the array's device address (cudaGetSymbolAddress); make that first call
+ *     outside any stream capture;
+ *   - all calls on a device share the one array and it keeps the previous call's contents (the words that must start
+ *     at zero are cleared at the start of every call): two calls that overlap on the GPU - different streams, or
+ *     different host threads - race. Serialise them on one stream;
+ *   - there is no backward for this entry point (nothing is kept for it).
+ * It calls no cudaMalloc, cudaFree or allocating library routine.
+ */
+#define CWRNNT_STATIC_MAX_ROWS 131072
+#define CWRNNT_STATIC_MAX_SEQUENCES 1024
+CWRNNT_API int cwrnnt_costs_static(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly,
+                                   const int32_t *y, void *costs, void *loss, cwrnnt_stream_t stream);
 
 /*
  * Host-buffer pipeline: logits, lengths and labels in HOST memory (pinned for overlap), costs / loss / gradients
