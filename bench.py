@@ -109,11 +109,19 @@ class ClockSampler:
                 "power_w_max": max(float(r[2]) for r in rows), "samples": len(rows), "reasons": reasons}
 
 
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_reference_time(cfg, lx, ly, y, n_seqs, budget_s=12.0):
     """The CPU checker's fused float32 pipeline (all host threads) on the first n_seqs sequences, repeated until
     about budget_s seconds of wall time are spent; nodes/s of the best repetition."""
     from oracle import oracle
     oracle.build()
+    oracle.set_num_threads(host_threads())
     import numpy as np
     ids = list(range(min(n_seqs, len(lx))))
     x = synth.compact_logits(cfg, lx, ly, ids).float().numpy()
@@ -141,6 +149,7 @@ def run_reference(args):
     n_seqs = args.cpu_sample_seqs
     from oracle import oracle
     oracle.build()
+    oracle.set_num_threads(host_threads())  # torch.distributed.run exports OMP_NUM_THREADS=1: use the cores anyway
     import numpy as np
     ids = list(range(min(n_seqs, len(lx))))
     x = synth.compact_logits(cfg, lx, ly, ids).float().numpy()
@@ -210,11 +219,18 @@ def main():
     gx = torch.empty_like(x)
     one = torch.ones(1, dtype=ct, device=dev)
     vec = torch.empty(B_global + 1, dtype=ct, device=dev)
+    ids_dev = torch.tensor(ids, dtype=torch.int32, device=dev)
+
+    def forward():
+        if world == 1:
+            capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
+        else:
+            # the wavefront epilogue fills the global cost vector; one all-reduce is the whole exchange
+            capi.forward_sharded(p, x, lxd, lyd, yd, ws, costs, loss, ids_dev, B_global, vec)
+            dist.all_reduce(vec, op=dist.ReduceOp.SUM)
 
     def step():
-        capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
-        if world > 1:
-            sharding.exchange_costs(costs, ids, B_global, local_loss=loss, out=vec)
+        forward()
         capi.backward(p, x, lxd, lyd, yd, ws, one, 0, gx)
 
     def fence():
@@ -237,9 +253,7 @@ def main():
     mark = sampler.mark() if sampler else 0
     for k in range(K):
         ev[k][0].record()
-        capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
-        if world > 1:
-            sharding.exchange_costs(costs, ids, B_global, local_loss=loss, out=vec)
+        forward()
         ev[k][1].record()
         capi.backward(p, x, lxd, lyd, yd, ws, one, 0, gx)
         ev[k][2].record()
@@ -291,7 +305,7 @@ def main():
                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
                "what": "cwrnnt_loss_grad_host: pinned host logits -> device (chunked, 3 streams) -> host gradients "
                        "and costs; per-rank bytes",
-               "loss": float(l_host)}
+               "loss": float(vec[B_global]) if world > 1 else float(l_host)}
         pipe.close()
 
     if rank != 0:

@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libcwarp_rnnt_b200.so")
+LIB_PATH = os.environ.get("CWRNNT_LIB") or os.path.join(_PKG, "libcwarp_rnnt_b200.so")  # override: another build
 
 F32, F16, BF16, F64 = 0, 1, 2, 3
 FUSED_LOG_SOFTMAX, COSTS_ONLY, REDUCE_MEAN, REDUCE_SUM, AVERAGE_FRAMES = 0x01, 0x02, 0x04, 0x08, 0x10
@@ -25,7 +25,7 @@ EXPORTS = [
     "cwrnnt_abi_version", "cwrnnt_status_string", "cwrnnt_last_error", "cwrnnt_workspace_bytes", "cwrnnt_forward",
     "cwrnnt_backward", "cwrnnt_pair_grads", "cwrnnt_export_alpha_beta", "cwrnnt_scatter_scratch_bytes",
     "cwrnnt_scatter_backward", "cwrnnt_read_status", "cwrnnt_host_ctx_create", "cwrnnt_host_ctx_destroy",
-    "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static",
+    "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
 ]
 
 
@@ -58,6 +58,7 @@ def lib():
         L.cwrnnt_workspace_bytes.restype = i64
         L.cwrnnt_workspace_bytes.argtypes = [pp]
         L.cwrnnt_forward.argtypes = [pp, vp, vp, vp, vp, vp, i64, vp, vp, vp]
+        L.cwrnnt_forward_sharded.argtypes = [pp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp, vp]
         L.cwrnnt_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
         L.cwrnnt_pair_grads.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_export_alpha_beta.argtypes = [pp, vp, vp, vp, i32, i32, vp, vp, vp]
@@ -126,6 +127,14 @@ def forward(p: Problem, x, lx, ly, y, workspace, costs, loss=None) -> None:
     with torch.cuda.device(x.device):
         check(lib().cwrnnt_forward(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
                                    workspace.numel(), _ptr(costs), _ptr(loss), _stream(x.device)), "cwrnnt_forward")
+
+
+def forward_sharded(p: Problem, x, lx, ly, y, workspace, costs, loss, global_ids, n_global, cost_vector) -> None:
+    """Forward of this rank's shard; also fills cost_vector [n_global + 1] for one all-reduce(sum) across ranks."""
+    with torch.cuda.device(x.device):
+        check(lib().cwrnnt_forward_sharded(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
+                                           workspace.numel(), _ptr(costs), _ptr(loss), _ptr(global_ids), n_global,
+                                           _ptr(cost_vector), _stream(x.device)), "cwrnnt_forward_sharded")
 
 
 def backward(p: Problem, x, lx, ly, y, workspace, grad_costs, grad_costs_stride, grad_x) -> None:

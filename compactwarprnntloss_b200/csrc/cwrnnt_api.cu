@@ -69,8 +69,9 @@ int64_t cwrnnt_workspace_bytes(const cwrnnt_problem *p)
     return carve_workspace(p->n_rows, p->B, nullptr, nullptr);
 }
 
-int cwrnnt_forward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
-                   void *workspace, int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream)
+static int forward_impl(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                        void *workspace, int64_t workspace_bytes, void *costs, void *loss, const ShardOutput *shard,
+                        cwrnnt_stream_t stream)
 {
     int st = check_problem(p);
     if (st) return st;
@@ -83,8 +84,23 @@ int cwrnnt_forward(const cwrnnt_problem *p, const void *x, const int32_t *lx, co
     cudaError_t e;
     if ((e = launch_prep(*p, lx, ly, w, costs, s)) != cudaSuccess) return fail_launch("prep", e);
     if ((e = launch_gather(*p, x, lx, ly, y, w, s)) != cudaSuccess) return fail_launch("gather", e);
-    if ((e = launch_wavefront(*p, lx, ly, w, costs, loss, s)) != cudaSuccess) return fail_launch("wavefront", e);
+    if ((e = launch_wavefront(*p, lx, ly, w, costs, loss, shard, s)) != cudaSuccess) return fail_launch("wavefront", e);
     return CWRNNT_OK;
+}
+
+int cwrnnt_forward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                   void *workspace, int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream)
+{
+    return forward_impl(p, x, lx, ly, y, workspace, workspace_bytes, costs, loss, nullptr, stream);
+}
+
+int cwrnnt_forward_sharded(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly,
+                           const int32_t *y, void *workspace, int64_t workspace_bytes, void *costs, void *loss,
+                           const int32_t *global_ids, int32_t n_global, void *cost_vector, cwrnnt_stream_t stream)
+{
+    if (!p || !cost_vector || n_global < p->B) return CWRNNT_ERR_ARGUMENT;
+    ShardOutput shard{global_ids, n_global, cost_vector};
+    return forward_impl(p, x, lx, ly, y, workspace, workspace_bytes, costs, loss, &shard, stream);
 }
 
 int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,

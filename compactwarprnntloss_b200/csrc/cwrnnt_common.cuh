@@ -23,7 +23,7 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; persistent grids are siz
 //   lse      : double [rows] log-sum-exp of each logits row (0 for log-prob input)
 //   lp_blank : double [rows] log P(blank | t,u), stored DIAGONAL-MAJOR inside each sequence (see diag_index)
 //   lp_label : double [rows] log P(y_u   | t,u), same order
-//   alpha    : double [rows] forward variables, (t,u) row-major like the logits rows
+//   alpha    : double [rows] forward variables, diagonal-major like lp_blank
 //   beta     : double [rows] backward variables, same order
 struct Workspace {
     int32_t *status;
@@ -99,6 +99,20 @@ __host__ __device__ inline int64_t diag_index(int t, int u, int T, int m)
     const int d = t + u;
     const int lo = d - (T - 1) > 0 ? d - (T - 1) : 0;
     return cells_before(d, T, m) + (u - lo);
+}
+
+// Positions, inside a sequence's diagonal-major arrays, of cell (t,u) and of its successor (t+1,u) on the next
+// diagonal; the other successor (t,u+1) sits right after the latter. The successor position is meaningful only when
+// that cell exists.
+__host__ __device__ inline void diag_cell_and_next(int t, int u, int T, int m, int64_t *cell, int64_t *next)
+{
+    const int d = t + u, U = m - 1;
+    const int lo = d - (T - 1) > 0 ? d - (T - 1) : 0;
+    const int hi = d < U ? d : U;
+    const int lo1 = d + 1 - (T - 1) > 0 ? d + 1 - (T - 1) : 0;
+    const int64_t before = cells_before(d, T, m);
+    *cell = before + (u - lo);
+    *next = before + (hi - lo + 1) + (u - lo1);
 }
 
 // ------------------------------------------------------------------------------------------------ element traits

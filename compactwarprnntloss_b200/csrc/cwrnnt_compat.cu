@@ -23,14 +23,16 @@ pair_grads_kernel(int64_t n_rows, int B, const int32_t *__restrict__ lx, const i
         const int T = lx[n], U = ly[n], m = U + 1;
         const unsigned rel = unsigned(r - off);
         const int t = int(rel / unsigned(m)), u = int(rel - unsigned(t) * unsigned(m));
-        const int64_t at = off + diag_index(t, u, T, m);
-        const double ll = w.ll_beta[n], a = w.alpha[r];
+        int64_t cell, next;
+        diag_cell_and_next(t, u, T, m, &cell, &next);
+        const int64_t at = off + cell;
+        const double ll = w.ll_beta[n], a = w.alpha[at];
         double gb = 0.0, gl = 0.0;
         if (t < T - 1)
-            gb = -exp(a + w.beta[r + m] + w.lp_blank[at] - ll);
+            gb = -exp(a + w.beta[off + next] + w.lp_blank[at] - ll);
         else if (u == U)
             gb = -exp(a + w.lp_blank[at] - ll);
-        if (u < U) gl = -exp(a + w.beta[r + 1] + w.lp_label[at] - ll);
+        if (u < U) gl = -exp(a + w.beta[off + next + 1] + w.lp_label[at] - ll);
         grads[2 * r] = CostT(gb);
         grads[2 * r + 1] = CostT(gl);
     }
@@ -51,7 +53,7 @@ export_ab_kernel(int B, int t_max, int u_max1, const int32_t *__restrict__ lx, c
         const int t = int(rem / u_max1), u = int(rem - int64_t(t) * u_max1);
         const int T = lx[n], U = ly[n];
         const bool in = t < T && u <= U;
-        const int64_t r = w.off[n] + int64_t(t) * (U + 1) + u;
+        const int64_t r = in ? w.off[n] + diag_index(t, u, T, U + 1) : 0;
         if (alphas) alphas[i] = in ? CostT(w.alpha[r]) : CostT(0);
         if (betas) betas[i] = in ? CostT(w.beta[r]) : CostT(0);
     }
@@ -68,19 +70,26 @@ scatter_kernel(int64_t n_rows, int V, int B, const int32_t *__restrict__ lx, con
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5;
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    int cursor = 0;
-    for (int64_t r = warp; r < n_rows; r += n_warps) {
-        RowInfo ri = locate_row(r, cursor, off, B, lx, ly, y, y_stride, V);
-        const CostT g = grad_costs[ri.n];
+    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
+    const int64_t r_begin = warp * per_warp;
+    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
+    if (r_begin >= r_end) return;
+    bool ignored = false;
+    RowWalker rw;
+    rw.start(r_begin, off, B, lx, ly);
+    for (int64_t r = r_begin; r < r_end; ++r) {
+        const int label = rw.label(y, y_stride, V, ignored);
+        const CostT g = grad_costs[rw.n];
         const CostT vb = grads[2 * r] * g;
-        const CostT vl = ri.label >= 0 ? grads[2 * r + 1] * g : CostT(0);
+        const CostT vl = label >= 0 ? grads[2 * r + 1] * g : CostT(0);
         CostT *row = dense + r * int64_t(V);
         for (int k = lane; k < V; k += 32) {
             CostT v = CostT(0);
             if (k == blank) v += vb;
-            if (k == ri.label) v += vl;
+            if (k == label) v += vl;
             __stcs(row + k, v);
         }
+        rw.advance(off, B, lx, ly);
     }
 }
 

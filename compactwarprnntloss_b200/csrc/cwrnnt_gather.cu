@@ -11,8 +11,10 @@
 
 namespace cwrnnt {
 
-// LPR lanes hold one row in registers (NV vectors of 16 bytes each); 32/LPR rows per warp.
-template <typename T, int LPR, int NV>
+// LPR lanes hold one row in registers (NV vectors of 16 bytes each); 32/LPR rows per warp. Every lane group owns one
+// contiguous run of rows (n_rows split evenly over all groups of the persistent grid), so its lattice position is
+// found once and then advanced incrementally. FULL: the row fills all LPR*NV vector slots (no per-vector predicate).
+template <typename T, int LPR, int NV, bool FULL, bool RUNS>
 __global__ void __launch_bounds__(kStreamThreads)
 gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const int32_t *__restrict__ lx,
                    const int32_t *__restrict__ ly, const int32_t *__restrict__ y, int y_stride, int blank,
@@ -21,39 +23,46 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
     using E = Elt<T>;
     using A = typename E::acc;
     constexpr int VE = E::VE;
-    constexpr int RPC = kStreamThreads / LPR;  // rows per CTA tile
+    constexpr int GPC = kStreamThreads / LPR;  // lane groups per CTA
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
-    const int gl = threadIdx.x % LPR;     // lane within the row group
-    const int grp = threadIdx.x / LPR;    // row slot within the CTA tile
+    const int gl = threadIdx.x % LPR;  // lane within the row group
     const int nvec = V / VE;
-    const int64_t n_tiles = (n_rows + RPC - 1) / RPC;
-    int cursor = 0;
+    // RUNS: every lane group owns one contiguous run of rows (n_rows split evenly over all groups).
+    // otherwise: a CTA takes GPC consecutive rows per iteration and strides over the matrix by the grid size.
+    const int64_t n_groups = int64_t(gridDim.x) * GPC;
+    const int64_t per_group = (n_rows + n_groups - 1) / n_groups;
+    const int64_t n_tiles = (n_rows + GPC - 1) / GPC;
+    const int64_t first = RUNS ? (int64_t(blockIdx.x) * GPC + threadIdx.x / LPR) * per_group
+                               : int64_t(blockIdx.x) * GPC + threadIdx.x / LPR;
+    const int64_t stride = RUNS ? 1 : n_groups;
+    const int64_t limit = RUNS ? (first + per_group < n_rows ? first + per_group : n_rows) : n_rows;
+    const int64_t iters = RUNS ? per_group : (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
     bool any_bad = false;
 
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t r = tile * RPC + grp;
-        const bool live = r < n_rows;
-        RowInfo ri{};
+    RowWalker rw;
+    for (int64_t i = 0; i < iters; ++i) {
+        const int64_t r = first + i * stride;
+        const bool live = r < limit;
         uint4 v[NV];
         A xb = A(0), xl = A(0);
+        int label = -1;
         if (live) {
-            ri = locate_row(r, cursor, w.off, B, lx, ly, y, y_stride, V);
+            if (i == 0) rw.start(r, w.off, B, lx, ly);
+            else if (!RUNS) rw.restart(r, w.off, B, lx, ly);
             const T *row = x + r * int64_t(V);
             const uint4 *rv = reinterpret_cast<const uint4 *>(row);
 #pragma unroll
-            for (int j = 0; j < NV; ++j) {
-                const int idx = j * LPR + gl;
-                if (idx < nvec) v[j] = ld_nc(rv + idx);
-            }
+            for (int j = 0; j < NV; ++j)
+                if (FULL || j * LPR + gl < nvec) v[j] = ld_nc(rv + j * LPR + gl);
+            label = rw.label(y, y_stride, V, any_bad);
             xb = E::to_acc(__ldg(row + blank));
-            if (ri.label >= 0) xl = E::to_acc(__ldg(row + ri.label));
-            any_bad |= ri.bad_label;
+            if (label >= 0) xl = E::to_acc(__ldg(row + label));
         }
         A mx = -INFINITY;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            if (live && j * LPR + gl < nvec) {
+            if (live && (FULL || j * LPR + gl < nvec)) {
                 A e[VE];
                 E::unpack(v[j], e);
 #pragma unroll
@@ -65,7 +74,7 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
         A sum = A(0);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            if (live && j * LPR + gl < nvec) {
+            if (live && (FULL || j * LPR + gl < nvec)) {
                 A e[VE];
                 E::unpack(v[j], e);
 #pragma unroll
@@ -73,12 +82,15 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
             }
         }
         sum = group_sum<LPR>(sum);
-        if (live && gl == 0) {
-            const double lse = shift.lse(sum);
-            const int64_t at = ri.off + diag_index(ri.t, ri.u, ri.T, ri.U + 1);
-            w.lse[r] = lse;
-            w.lp_blank[at] = double(xb) - lse;
-            if (ri.label >= 0) w.lp_label[at] = double(xl) - lse;
+        if (live) {
+            if (gl == 0) {
+                const double lse = shift.lse(sum);
+                const int64_t at = rw.off + rw.at;
+                w.lse[r] = lse;
+                w.lp_blank[at] = double(xb) - lse;
+                if (label >= 0) w.lp_label[at] = double(xl) - lse;
+            }
+            if (RUNS) rw.advance(w.off, B, lx, ly);
         }
     }
     if (any_bad) atomicOr(w.status, CWRNNT_ST_BAD_LABEL);
@@ -95,13 +107,15 @@ gather_rows_generic_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B
     using A = typename E::acc;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5;
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    int cursor = 0;
+    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
+    const int64_t r_begin = ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
+    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
     bool any_bad = false;
-    for (int64_t r = warp; r < n_rows; r += n_warps) {
-        RowInfo ri = locate_row(r, cursor, w.off, B, lx, ly, y, y_stride, V);
-        any_bad |= ri.bad_label;
+    RowWalker rw;
+    if (r_begin < r_end) rw.start(r_begin, w.off, B, lx, ly);
+    for (int64_t r = r_begin; r < r_end; ++r) {
+        const int label = rw.label(y, y_stride, V, any_bad);
         const T *row = x + r * int64_t(V);
         A mx = -INFINITY;
         for (int k = lane; k < V; k += 32) {
@@ -115,16 +129,17 @@ gather_rows_generic_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B
         sum = group_sum<32>(sum);
         if (lane == 0) {
             const double lse = shift.lse(sum);
-            const int64_t at = ri.off + diag_index(ri.t, ri.u, ri.T, ri.U + 1);
+            const int64_t at = rw.off + rw.at;
             w.lse[r] = lse;
             w.lp_blank[at] = double(E::to_acc(__ldg(row + blank))) - lse;
-            if (ri.label >= 0) w.lp_label[at] = double(E::to_acc(__ldg(row + ri.label))) - lse;
+            if (label >= 0) w.lp_label[at] = double(E::to_acc(__ldg(row + label))) - lse;
         }
+        rw.advance(w.off, B, lx, ly);
     }
     if (any_bad) atomicOr(w.status, CWRNNT_ST_BAD_LABEL);
 }
 
-// Log-probability input (the reference contract): no normalisation, two elements per row, one thread per row.
+// Log-probability input (the reference contract): no normalisation, two elements per row, one thread per row run.
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
 gather_pair_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const int32_t *__restrict__ lx,
@@ -133,17 +148,19 @@ gather_pair_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
 {
     using E = Elt<T>;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
-    int cursor = 0;
     bool any_bad = false;
+    // consecutive threads take consecutive rows (the two 8-byte results per row then coalesce per warp); each thread
+    // strides by the grid size, so its position is re-located per row
     const int64_t stride = int64_t(gridDim.x) * kStreamThreads;
     for (int64_t r = int64_t(blockIdx.x) * kStreamThreads + threadIdx.x; r < n_rows; r += stride) {
-        RowInfo ri = locate_row(r, cursor, w.off, B, lx, ly, y, y_stride, V);
-        any_bad |= ri.bad_label;
+        RowWalker rw;
+        rw.start(r, w.off, B, lx, ly);
+        const int label = rw.label(y, y_stride, V, any_bad);
         const T *row = x + r * int64_t(V);
-        const int64_t at = ri.off + diag_index(ri.t, ri.u, ri.T, ri.U + 1);
+        const int64_t at = rw.off + rw.at;
         w.lse[r] = 0.0;
         w.lp_blank[at] = double(E::to_acc(__ldg(row + blank)));
-        if (ri.label >= 0) w.lp_label[at] = double(E::to_acc(__ldg(row + ri.label)));
+        if (label >= 0) w.lp_label[at] = double(E::to_acc(__ldg(row + label)));
     }
     if (any_bad) atomicOr(w.status, CWRNNT_ST_BAD_LABEL);
 }
@@ -154,10 +171,9 @@ static cudaError_t launch_gather_t(const cwrnnt_problem &p, const T *x, const in
 {
     if (p.n_rows == 0) return cudaSuccess;
     constexpr int VE = Elt<T>::VE;
-    const int max_ctas = kNumSMs * 8;
     if (!(p.flags & CWRNNT_FUSED_LOG_SOFTMAX)) {
-        int64_t tiles = (p.n_rows + kStreamThreads - 1) / kStreamThreads;
-        int grid = int(tiles < max_ctas ? tiles : max_ctas);
+        const int64_t tiles = (p.n_rows + kStreamThreads - 1) / kStreamThreads;
+        const int grid = int(tiles < kNumSMs * 8 ? tiles : kNumSMs * 8);
         gather_pair_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, w);
         return cudaGetLastError();
     }
@@ -165,19 +181,28 @@ static cudaError_t launch_gather_t(const cwrnnt_problem &p, const T *x, const in
     const bool vec_ok = (p.V % VE == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                         pick_row_shape(p.V / VE, &shape);
     if (vec_ok) {
-#define CALL(LPR, NV)                                                                                             \
-    {                                                                                                             \
-        const int rpc = kStreamThreads / LPR;                                                                     \
-        int64_t tiles = (p.n_rows + rpc - 1) / rpc;                                                               \
-        int grid = int(tiles < max_ctas ? tiles : max_ctas);                                                      \
-        gather_rows_kernel<T, LPR, NV><<<grid, kStreamThreads, 0, s>>>(x, p.V, p.n_rows, p.B, lx, ly, y,          \
-                                                                       p.y_stride, p.blank, w);                   \
+        const bool full = (p.V / VE) == shape.lpr * shape.nv;
+        // contiguous row runs per lane group: measured faster than CTA-strided tiles on every workload (fewer
+        // instructions per row; this kernel is close to issue-bound)
+        const bool runs = true;
+#define LAUNCH(LPR, NV, FULL, RUNS)                                                                                \
+    {                                                                                                              \
+        static const int grid = resident_grid(gather_rows_kernel<T, LPR, NV, FULL, RUNS>, kStreamThreads);         \
+        gather_rows_kernel<T, LPR, NV, FULL, RUNS><<<grid, kStreamThreads, 0, s>>>(x, p.V, p.n_rows, p.B, lx, ly,  \
+                                                                                   y, p.y_stride, p.blank, w);     \
+    }
+#define CALL(LPR, NV)                                \
+    {                                                \
+        if (full && runs) LAUNCH(LPR, NV, true, true)        \
+        else if (full) LAUNCH(LPR, NV, true, false)          \
+        else if (runs) LAUNCH(LPR, NV, false, true)          \
+        else LAUNCH(LPR, NV, false, false)                   \
     }
         CWRNNT_DISPATCH_SHAPE(shape, CALL);
 #undef CALL
+#undef LAUNCH
     } else {
-        int64_t tiles = (p.n_rows + 7) / 8;
-        int grid = int(tiles < max_ctas ? tiles : max_ctas);
+        static const int grid = resident_grid(gather_rows_generic_kernel<T>, kStreamThreads);
         gather_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
                                                                       p.blank, w);
     }

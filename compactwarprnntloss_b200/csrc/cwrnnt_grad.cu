@@ -23,27 +23,30 @@ __device__ __forceinline__ double occupancy(double e, float) { return double(exp
 __device__ __forceinline__ double occupancy(double e, double) { return exp(e); }
 
 // Occupancy terms of one row from the saved forward state. lpb/lpl: log-probs of blank / label at this cell.
+// alpha and beta are stored diagonal-major: (t,u) at rw.at, both successors side by side on the next diagonal.
 template <typename CostT>
-__device__ __forceinline__ void row_terms(const RowInfo &ri, int64_t r, const Workspace &w, double lpb, double lpl,
+__device__ __forceinline__ void row_terms(const RowWalker &rw, const Workspace &w, double lpb, double lpl,
                                           const CostT *__restrict__ grad_costs, int gc_stride, int flags,
                                           double mean_inv, double &wb, double &wl)
 {
-    const int m = ri.U + 1;
-    const double ll = __ldg(w.ll_beta + ri.n);
-    const double a = __ldg(w.alpha + r);
+    const double *beta_next = w.beta + rw.off + rw.next_diag();
+    const double ll = __ldg(w.ll_beta + rw.n);
+    const double a = __ldg(w.alpha + rw.off + rw.at);
     double eb = -INFINITY, el = -INFINITY;
-    if (ri.t < ri.T - 1)
-        eb = a + __ldg(w.beta + r + m) + lpb - ll;
-    else if (ri.u == ri.U)
+    if (rw.t < rw.T - 1)
+        eb = a + __ldg(beta_next) + lpb - ll;
+    else if (rw.u == rw.U)
         eb = a + lpb - ll;
-    if (ri.u < ri.U) el = a + __ldg(w.beta + r + 1) + lpl - ll;
-    double g = grad_costs ? double(__ldg(grad_costs + int64_t(ri.n) * gc_stride)) : 1.0;
-    g *= sequence_scale(flags, ri.T) * mean_inv;
+    if (rw.u < rw.U) el = a + __ldg(beta_next + 1) + lpl - ll;
+    double g = grad_costs ? double(__ldg(grad_costs + int64_t(rw.n) * gc_stride)) : 1.0;
+    g *= sequence_scale(flags, rw.T) * mean_inv;
     wb = g * occupancy(eb, CostT(0));
     wl = g * occupancy(el, CostT(0));
 }
 
-template <typename T, int LPR, int NV>
+// Same row shapes and row runs as the gather kernel. No warp-wide collective is needed here: each lane scales its own
+// part of the row by the row's occupancy sum.
+template <typename T, int LPR, int NV, bool FULL, bool RUNS>
 __global__ void __launch_bounds__(kStreamThreads)
 grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_rows, int B,
                  const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, const int32_t *__restrict__ y,
@@ -54,55 +57,60 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_r
     using A = typename E::acc;
     using CostT = typename E::cost;
     constexpr int VE = E::VE;
-    constexpr int RPC = kStreamThreads / LPR;
+    constexpr int GPC = kStreamThreads / LPR;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
     const int gl = threadIdx.x % LPR;
-    const int grp = threadIdx.x / LPR;
     const int nvec = V / VE;
-    const int64_t n_tiles = (n_rows + RPC - 1) / RPC;
-    int cursor = 0;
+    // RUNS: every lane group owns one contiguous run of rows; otherwise a CTA takes GPC consecutive rows per
+    // iteration and strides over the matrix by the grid size (fewer DRAM pages open at once).
+    const int64_t n_groups = int64_t(gridDim.x) * GPC;
+    const int64_t per_group = (n_rows + n_groups - 1) / n_groups;
+    const int64_t first = RUNS ? (int64_t(blockIdx.x) * GPC + threadIdx.x / LPR) * per_group
+                               : int64_t(blockIdx.x) * GPC + threadIdx.x / LPR;
+    const int64_t stride = RUNS ? 1 : n_groups;
+    const int64_t limit = RUNS ? (first + per_group < n_rows ? first + per_group : n_rows) : n_rows;
+    bool ignored = false;
 
-    for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const int64_t r = tile * RPC + grp;
-        if (r >= n_rows) continue;  // no warp-wide collectives below: each lane works alone
-        RowInfo ri = locate_row(r, cursor, w.off, B, lx, ly, y, y_stride, V);
+    RowWalker rw;
+    for (int64_t r = first; r < limit; r += stride) {
+        if (r == first) rw.start(r, w.off, B, lx, ly);
+        else if (!RUNS) rw.restart(r, w.off, B, lx, ly);
         const T *row = x + r * int64_t(V);
         T *orow = gx + r * int64_t(V);
         const uint4 *rv = reinterpret_cast<const uint4 *>(row);
         uint4 *ov = reinterpret_cast<uint4 *>(orow);
         uint4 v[NV];
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            const int idx = j * LPR + gl;
-            if (idx < nvec) v[j] = ld_stream(rv + idx);
-        }
+        for (int j = 0; j < NV; ++j)
+            if (FULL || j * LPR + gl < nvec) v[j] = ld_stream(rv + j * LPR + gl);
+        const int label = rw.label(y, y_stride, V, ignored);
         const A xb = E::to_acc(__ldg(row + blank));
-        const A xl = ri.label >= 0 ? E::to_acc(__ldg(row + ri.label)) : A(0);
+        const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
         const double lse = __ldg(w.lse + r);
         double wb, wl;
-        row_terms<CostT>(ri, r, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
+        row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
         const A tot = A(wb + wl);
         const A lse_a = A(lse);
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
-            const int idx = j * LPR + gl;
-            if (idx < nvec) {
+            if (FULL || j * LPR + gl < nvec) {
                 A e[VE];
                 E::unpack(v[j], e);
 #pragma unroll
                 for (int c = 0; c < VE; ++c) e[c] = exp_shifted(e[c], lse_a) * tot;
-                st_stream(ov + idx, E::pack(e));
+                st_stream(ov + j * LPR + gl, E::pack(e));
             }
         }
         // the two sparse corrections, by the lane that stored the enclosing vector (same-thread program order)
         if ((blank / VE) % LPR == gl) {
             A gb = exp_shifted(xb, lse_a) * tot - A(wb);
-            if (ri.label == blank) gb -= A(wl);
+            if (label == blank) gb -= A(wl);
             orow[blank] = E::from_acc(gb);
         }
-        if (ri.label >= 0 && ri.label != blank && (ri.label / VE) % LPR == gl)
-            orow[ri.label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
+        if (label >= 0 && label != blank && (label / VE) % LPR == gl)
+            orow[label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
+        if (RUNS) rw.advance(w.off, B, lx, ly);
     }
 }
 
@@ -119,25 +127,31 @@ grad_rows_generic_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int
     using CostT = typename E::cost;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5;
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    int cursor = 0;
-    for (int64_t r = warp; r < n_rows; r += n_warps) {
-        RowInfo ri = locate_row(r, cursor, w.off, B, lx, ly, y, y_stride, V);
+    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
+    const int64_t r_begin = ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
+    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
+    if (r_begin >= r_end) return;
+    bool ignored = false;
+    RowWalker rw;
+    rw.start(r_begin, w.off, B, lx, ly);
+    for (int64_t r = r_begin; r < r_end; ++r) {
         const T *row = x + r * int64_t(V);
         T *orow = gx + r * int64_t(V);
+        const int label = rw.label(y, y_stride, V, ignored);
         const A xb = E::to_acc(__ldg(row + blank));
-        const A xl = ri.label >= 0 ? E::to_acc(__ldg(row + ri.label)) : A(0);
+        const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
         const double lse = __ldg(w.lse + r);
         double wb, wl;
-        row_terms<CostT>(ri, r, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
+        row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
         const A tot = A(wb + wl), lse_a = A(lse);
         for (int k = lane; k < V; k += 32) {
             A g = exp_shifted(E::to_acc(__ldg(row + k)), lse_a) * tot;
             if (k == blank) g -= A(wb);
-            if (k == ri.label) g -= A(wl);
+            if (k == label) g -= A(wl);
             orow[k] = E::from_acc(g);
         }
+        rw.advance(w.off, B, lx, ly);
     }
 }
 
@@ -155,33 +169,38 @@ grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int6
     constexpr int VE = E::VE;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
     const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5;
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    int cursor = 0;
-    for (int64_t r = warp; r < n_rows; r += n_warps) {
-        RowInfo ri = locate_row(r, cursor, w.off, B, lx, ly, y, y_stride, V);
+    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
+    const int64_t r_begin = ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
+    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
+    if (r_begin >= r_end) return;
+    bool ignored = false;
+    RowWalker rw;
+    rw.start(r_begin, w.off, B, lx, ly);
+    for (int64_t r = r_begin; r < r_end; ++r) {
         const T *row = x + r * int64_t(V);
         T *orow = gx + r * int64_t(V);
+        const int label = rw.label(y, y_stride, V, ignored);
         const A xb = E::to_acc(__ldg(row + blank));
-        const A xl = ri.label >= 0 ? E::to_acc(__ldg(row + ri.label)) : A(0);
+        const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
         double wb, wl;
-        row_terms<CostT>(ri, r, w, double(xb), double(xl), grad_costs, gc_stride, flags, mean_inv, wb, wl);
+        row_terms<CostT>(rw, w, double(xb), double(xl), grad_costs, gc_stride, flags, mean_inv, wb, wl);
         if (vec_ok) {
             uint4 *ov = reinterpret_cast<uint4 *>(orow);
             const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
             for (int idx = lane; idx < V / VE; idx += 32) st_stream(ov + idx, zero);
             // the lane that zeroed the enclosing vector writes the sparse term afterwards
-            if ((blank / VE) % 32 == lane) orow[blank] = E::from_acc(A(-(wb + (ri.label == blank ? wl : 0.0))));
-            if (ri.label >= 0 && ri.label != blank && (ri.label / VE) % 32 == lane)
-                orow[ri.label] = E::from_acc(A(-wl));
+            if ((blank / VE) % 32 == lane) orow[blank] = E::from_acc(A(-(wb + (label == blank ? wl : 0.0))));
+            if (label >= 0 && label != blank && (label / VE) % 32 == lane) orow[label] = E::from_acc(A(-wl));
         } else {
             for (int k = lane; k < V; k += 32) {
                 A g = A(0);
                 if (k == blank) g -= A(wb);
-                if (k == ri.label) g -= A(wl);
+                if (k == label) g -= A(wl);
                 orow[k] = E::from_acc(g);
             }
         }
+        rw.advance(w.off, B, lx, ly);
     }
 }
 
@@ -193,15 +212,13 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     using CostT = typename Elt<T>::cost;
     if (p.n_rows == 0) return cudaSuccess;
     constexpr int VE = Elt<T>::VE;
-    const int max_ctas = kNumSMs * 8;
     const CostT *gc = static_cast<const CostT *>(grad_costs);
     const double mean_inv =
         (p.flags & CWRNNT_REDUCE_MEAN) ? 1.0 / double(p.mean_denominator > 0 ? p.mean_denominator : p.B) : 1.0;
     const bool aligned = (p.V % VE == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                          (reinterpret_cast<uintptr_t>(gx) % 16 == 0);
-    int64_t tiles = (p.n_rows + 7) / 8;
-    int grid = int(tiles < max_ctas ? tiles : max_ctas);
     if (!(p.flags & CWRNNT_FUSED_LOG_SOFTMAX)) {
+        static const int grid = resident_grid(grad_rows_sparse_kernel<T>, kStreamThreads);
         grad_rows_sparse_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
                                                                    p.blank, p.flags, mean_inv, w, gc, gc_stride,
                                                                    aligned ? 1 : 0);
@@ -209,18 +226,31 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     }
     RowShape shape{};
     if (aligned && pick_row_shape(p.V / VE, &shape)) {
-#define CALL(LPR, NV)                                                                                              \
-    {                                                                                                              \
-        const int rpc = kStreamThreads / LPR;                                                                      \
-        tiles = (p.n_rows + rpc - 1) / rpc;                                                                        \
-        grid = int(tiles < max_ctas ? tiles : max_ctas);                                                           \
-        grad_rows_kernel<T, LPR, NV><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y,         \
-                                                                     p.y_stride, p.blank, p.flags, mean_inv, w, gc, \
-                                                                     gc_stride);                                   \
+        const bool full = (p.V / VE) == shape.lpr * shape.nv;
+        // Row assignment, measured on B200: rows of 2 KB and more stream best when a CTA takes 8 consecutive rows per
+        // iteration and strides by the grid (443 us vs 455 us at V=1024 float32: fewer DRAM pages open at once for
+        // the mixed read/write stream); short rows are bound by per-row instructions and prefer contiguous runs
+        // (435 us vs 575 us at V=128 float16).
+        const bool runs = int64_t(p.V) * int64_t(sizeof(T)) < 2048;
+#define LAUNCH(LPR, NV, FULL, RUNS)                                                                               \
+    {                                                                                                             \
+        static const int resident = resident_grid(grad_rows_kernel<T, LPR, NV, FULL, RUNS>, kStreamThreads);      \
+        const int grid = RUNS ? resident : 2 * resident; /* strided tiles: two waves even out the tail */         \
+        grad_rows_kernel<T, LPR, NV, FULL, RUNS><<<grid, kStreamThreads, 0, s>>>(                                 \
+            x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride);      \
+    }
+#define CALL(LPR, NV)                                \
+    {                                                \
+        if (full && runs) LAUNCH(LPR, NV, true, true)        \
+        else if (full) LAUNCH(LPR, NV, true, false)          \
+        else if (runs) LAUNCH(LPR, NV, false, true)          \
+        else LAUNCH(LPR, NV, false, false)                   \
     }
         CWRNNT_DISPATCH_SHAPE(shape, CALL);
 #undef CALL
+#undef LAUNCH
     } else {
+        static const int grid = resident_grid(grad_rows_generic_kernel<T>, kStreamThreads);
         grad_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
                                                                     p.blank, p.flags, mean_inv, w, gc, gc_stride);
     }

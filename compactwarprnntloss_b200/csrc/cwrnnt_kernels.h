@@ -17,9 +17,16 @@ cudaError_t launch_offsets_only(const int32_t *lx, const int32_t *ly, int B, int
 cudaError_t launch_gather(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
                           const int32_t *y, const Workspace &w, cudaStream_t s);
 
+// Sharded runs: where the costs go besides the local [B] array (see cwrnnt_forward_sharded).
+struct ShardOutput {
+    const int32_t *global_ids;  // [B] global slot of each local sequence, or nullptr for the identity
+    int32_t n_global;           // number of sequences over all ranks
+    void *cost_vector;          // [n_global + 1], costs type
+};
+
 // K2: alpha/beta anti-diagonal wavefront, costs, loss.
 cudaError_t launch_wavefront(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                             void *costs, void *loss, cudaStream_t s);
+                             void *costs, void *loss, const ShardOutput *shard, cudaStream_t s);
 
 // K3: dense gradient in one streaming pass.
 cudaError_t launch_grad(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,

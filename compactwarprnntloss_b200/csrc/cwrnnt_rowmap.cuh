@@ -1,4 +1,4 @@
-// Row -> (sequence, frame, column) mapping and vector-shape dispatch shared by the two streaming kernels. Internal.
+// Row -> (sequence, frame, column) bookkeeping and vector-shape dispatch shared by the two streaming kernels. Internal.
 #pragma once
 #include "cwrnnt_common.cuh"
 
@@ -6,40 +6,100 @@ namespace cwrnnt {
 
 constexpr int kStreamThreads = 256;  // 8 warps per CTA in the streaming kernels
 
-struct RowInfo {
+// Position of one lattice row while a group of lanes walks a contiguous run of rows. Found once per run by bisection
+// and one division, then advanced with a handful of integer operations per row - rows are visited in memory order,
+// which is (sequence, t, u) order.
+struct RowWalker {
     int n;        // sequence
     int T, U;     // its lengths
-    int t, u;     // lattice cell of this row
-    int64_t off;  // first row of the sequence
-    int label;    // y[n][u] clamped into [0,V), or -1 when u == U
-    bool bad_label;
-};
+    int t, u;     // lattice cell of the current row
+    int64_t off;  // first row of the sequence (also the base of its diagonal-major arrays)
+    int64_t at;   // diagonal-major position of (t,u) inside the sequence
 
-__device__ __forceinline__ RowInfo locate_row(int64_t r, int &cursor, const int64_t *__restrict__ off, int B,
-                                              const int32_t *__restrict__ lx, const int32_t *__restrict__ ly,
-                                              const int32_t *__restrict__ y, int y_stride, int V)
-{
-    RowInfo ri;
-    ri.n = cursor = find_sequence(off, B, r, cursor);
-    ri.off = __ldg(off + ri.n);
-    ri.T = __ldg(lx + ri.n);
-    ri.U = __ldg(ly + ri.n);
-    const unsigned rel = unsigned(r - ri.off);  // a sequence has fewer than 2^31 cells
-    const unsigned m = unsigned(ri.U) + 1u;
-    ri.t = int(rel / m);
-    ri.u = int(rel - unsigned(ri.t) * m);
-    ri.label = -1;
-    ri.bad_label = false;
-    if (ri.u < ri.U) {
-        int k = __ldg(y + int64_t(ri.n) * y_stride + ri.u);
+    __device__ __forceinline__ void start(int64_t r, const int64_t *__restrict__ offs, int B,
+                                          const int32_t *__restrict__ lx, const int32_t *__restrict__ ly)
+    {
+        int lo = 0, hi = B;  // invariant: offs[lo] <= r < offs[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (r >= __ldg(offs + mid))
+                lo = mid;
+            else
+                hi = mid;
+        }
+        n = lo;
+        load_sequence(offs, lx, ly);
+        const unsigned rel = unsigned(r - off);  // a sequence has fewer than 2^31 cells
+        const unsigned m = unsigned(U) + 1u;
+        t = int(rel / m);
+        u = int(rel - unsigned(t) * m);
+        at = diag_index(t, u, T, U + 1);
+    }
+    // Same for a later row when the walker already stands on an earlier one: a short forward walk over the sequence
+    // boundaries (rows visited with a fixed stride usually stay in the same sequence or move to the next), bisection
+    // only after a long jump.
+    __device__ __forceinline__ void restart(int64_t r, const int64_t *__restrict__ offs, int B,
+                                            const int32_t *__restrict__ lx, const int32_t *__restrict__ ly)
+    {
+        int steps = 0;
+        while (n + 1 < B && r >= __ldg(offs + n + 1)) {
+            ++n;
+            if (++steps == 4) {
+                start(r, offs, B, lx, ly);
+                return;
+            }
+        }
+        if (steps) load_sequence(offs, lx, ly);
+        const unsigned rel = unsigned(r - off);
+        const unsigned m = unsigned(U) + 1u;
+        t = int(rel / m);
+        u = int(rel - unsigned(t) * m);
+        at = diag_index(t, u, T, U + 1);
+    }
+    __device__ __forceinline__ void load_sequence(const int64_t *__restrict__ offs, const int32_t *__restrict__ lx,
+                                                  const int32_t *__restrict__ ly)
+    {
+        off = __ldg(offs + n);
+        T = __ldg(lx + n);
+        U = __ldg(ly + n);
+    }
+    // Label of the current row clamped into [0,V), or -1 in the last column; reports an out-of-range label.
+    __device__ __forceinline__ int label(const int32_t *__restrict__ y, int y_stride, int V, bool &bad) const
+    {
+        if (u >= U) return -1;
+        int k = __ldg(y + int64_t(n) * y_stride + u);
         if (k < 0 || k >= V) {
-            ri.bad_label = true;
+            bad = true;
             k = k < 0 ? 0 : V - 1;
         }
-        ri.label = k;
+        return k;
     }
-    return ri;
-}
+    // Diagonal-major position of the successor (t+1,u); (t,u+1) is the element after it.
+    __device__ __forceinline__ int64_t next_diag() const
+    {
+        const int d = t + u;
+        const int lo0 = max(0, d - (T - 1)), lo1 = max(0, d + 1 - (T - 1));
+        return at + (min(d, U) - lo0 + 1) - (lo1 - lo0);
+    }
+    // Move to the next row in memory order. `more` = the run continues (avoids reading past the last sequence).
+    __device__ __forceinline__ void advance(const int64_t *__restrict__ offs, int B, const int32_t *__restrict__ lx,
+                                            const int32_t *__restrict__ ly)
+    {
+        if (u < U) {
+            // (t,u) on diagonal d -> (t,u+1) on diagonal d+1
+            const int d = t + u;
+            at += min(d, U) + 2 - max(0, d + 1 - (T - 1));
+            ++u;
+            return;
+        }
+        u = 0;
+        if (++t == T) {
+            t = 0;
+            if (++n < B) load_sequence(offs, lx, ly);
+        }
+        at = diag_index(t, 0, T, U + 1);
+    }
+};
 
 // Shape of the register-resident row: LPR lanes cooperate on one row, each holding NV 16-byte vectors.
 // Chosen from the number of vectors in a row; returns false when the row does not fit (generic path).
@@ -70,6 +130,17 @@ __host__ inline bool pick_row_shape(int64_t nvec, RowShape *s)
         else if ((shape).lpr == 32 && (shape).nv == 8) { CALL(32, 8); } \
         else { CALL(32, 16); }                                  \
     } while (0)
+
+// Persistent grid: as many CTAs as are resident at once (148 SMs x occupancy), so that the static, perfectly balanced
+// split of rows over lane groups runs as a single wave.
+template <typename K>
+__host__ inline int resident_grid(K kernel, int threads)
+{
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1)
+        per_sm = 4;
+    return kNumSMs * per_sm;
+}
 
 template <int LPR, typename A>
 __device__ __forceinline__ A group_max(A v)

@@ -90,7 +90,7 @@ extern "C" int cwrnnt_costs_static(const cwrnnt_problem *p, const void *x, const
     e = cudaGetLastError();
     if (e == cudaSuccess) what = "prep", e = launch_prep(q, lx, ly, w, costs, s);
     if (e == cudaSuccess) what = "gather", e = launch_gather(q, x, lx, ly, y, w, s);
-    if (e == cudaSuccess) what = "wavefront", e = launch_wavefront(q, lx, ly, w, costs, loss, s);
+    if (e == cudaSuccess) what = "wavefront", e = launch_wavefront(q, lx, ly, w, costs, loss, nullptr, s);
     if (e != cudaSuccess) {
         char msg[160];
         std::snprintf(msg, sizeof msg, "cwrnnt_costs_static %s: %s", what, cudaGetErrorString(e));

@@ -7,9 +7,14 @@
 //   alpha(t,u) = LSE(alpha(t-1,u) + blank(t-1,u), alpha(t,u-1) + label(t,u-1)),  alpha(0,0) = 0     (:59-125)
 //   beta(t,u)  = LSE(beta(t+1,u) + blank(t,u),    beta(t,u+1) + label(t,u)),     beta(T-1,U) = blank(T-1,U)  (:165-231)
 // The own-column operand stays in a register, the neighbour column arrives by warp shuffle (shared memory only at warp
-// seams, one named barrier per diagonal), and the log-probs stream in from the diagonal-major arrays K1 wrote, fully
-// coalesced and prefetched a few diagonals ahead of the dependent chain. alpha and beta CTAs of all sequences run
-// concurrently in one launch, longest critical path first.
+// seams, one named barrier per diagonal). The log-probs K1 wrote diagonal-major are one contiguous stream per
+// (sequence, direction): each thread stages its own operands, several diagonals ahead of the dependent chain, with
+// 8-byte cp.async copies into a shared-memory ring (fully coalesced across the warp, and no register scoreboard is
+// held while they fly). alpha and beta are written diagonal-major too, so a warp's store is one contiguous 256-byte
+// segment. alpha and beta CTAs of all sequences run concurrently in one launch, longest critical path first.
+// (A producer/consumer variant - one elected thread feeding the ring with cp.async.bulk + mbarrier - was built and
+// measured: 125 us against 79 us on the 81-column workload, because its per-step chunk bookkeeping costs more
+// instructions on the dependent chain than the per-thread copies it replaces; it was dropped.)
 //
 // Arithmetic: the running sums are kept in double (|alpha| reaches 10^3..10^4, where a float ulp is ~1e-4 and would
 // show up directly in exp(alpha+beta-ll)); the bounded correction log1p(exp(-|a-b|)) is evaluated in float as in the
@@ -17,6 +22,7 @@
 //
 // Bound: latency of the dependent chain, T+U steps per sequence; reported as microseconds per diagonal.
 // The last CTA to finish turns the per-sequence log-likelihoods into costs, the status bits and the reduced loss.
+#include <climits>
 #include <cstdio>
 #include <type_traits>
 
@@ -32,13 +38,30 @@ __device__ __forceinline__ void cta_sync(int n_active)
         __syncwarp();
 }
 
-// log(exp(a) + exp(b)) for the recursion. The float flavour keeps the running value in double and evaluates only the
-// bounded correction log1p(exp(-|a-b|)) in float, with the accurate expf/log1pf (about 1 ulp each: measured gradient
-// error stays below 1e-6 on lattices of 3000 diagonals, where the MUFU-approximate ex2/lg2 pair drifted past 1e-5);
-// the select of the larger operand runs beside it, off the dependent chain. -inf operands (absent move, masked
-// vocabulary entry) are handled: |a-b| = inf gives a zero correction, and the NaN of (-inf) - (-inf) is clamped away.
+// log(exp(a) + exp(b)) for the recursion: the larger operand plus the bounded correction
+//     f(g) = log1p(exp(-g)),  g = |a - b| >= 0,  f in (0, ln 2].
+// The running values stay in double. For float-type inputs f is read from a per-CTA shared-memory table instead of
+// calling expf/log1pf: nodes every 1/16 up to g = 32, four Taylor coefficients per node (f and its first three
+// derivatives over 1, 1, 2, 6, computed in double when the CTA starts), evaluated by a 3-FMA Horner step on
+// |h| <= 1/32. Truncation error is below 5e-9, total error below 6e-8 absolute with no measurable bias (the libm pair
+// log1pf(expf()) is at 1.1e-7), and it costs 10 instructions on the dependent chain instead of about 40 - the chain's
+// length is what bounds this kernel. -inf operands (absent move, masked vocabulary entry) need no branch: g clamps to
+// 32 (f = 1.3e-14), the NaN of (-inf) - (-inf) is dropped by fminf, and -inf plus a finite correction stays -inf.
+constexpr int kLseNodes = 513;            // g = 0, 1/16, ..., 32
+constexpr float kLseMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to the nearest integer in the low mantissa bits
+
+__device__ __forceinline__ void build_lse_table(float4 *tab, int tid, int n_threads)
+{
+    for (int i = tid; i < kLseNodes; i += n_threads) {
+        const double g = double(i) * 0.0625;
+        const double s = 1.0 / (1.0 + exp(g));  // minus the first derivative
+        tab[i] = make_float4(float(log1p(exp(-g))), float(-s), float(0.5 * s * (1.0 - s)),
+                             float(-s * (1.0 - s) * (1.0 - 2.0 * s) / 6.0));
+    }
+}
+
 template <bool F64>
-__device__ __forceinline__ double lse2(double a, double b)
+__device__ __forceinline__ double lse2(double a, double b, const float4 *__restrict__ tab)
 {
     if (F64) {
         const double hi = fmax(a, b), lo = fmin(a, b);
@@ -46,9 +69,13 @@ __device__ __forceinline__ double lse2(double a, double b)
         return hi + log1p(exp(lo - hi));
     }
     const double diff = a - b;
-    const float gap = fminf(fabsf(__double2float_rn(diff)), 3.0e38f);  // fminf drops a NaN operand
+    const float g = fminf(fabsf(__double2float_rn(diff)), 32.0f);  // fminf drops a NaN operand
+    const float q = fmaf(g, 16.0f, kLseMagic);
+    const float4 t = tab[__float_as_int(q) & 0x3ff];
+    const float h = fmaf(q - kLseMagic, -0.0625f, g);
+    const float c = fmaf(fmaf(fmaf(t.w, h, t.z), h, t.y), h, t.x);
     const double hi = diff > 0.0 ? a : b;
-    return hi + double(log1pf(expf(-gap)));
+    return hi + double(c);
 }
 
 __device__ __forceinline__ void cp_async8(void *smem_dst, const void *gmem_src)
@@ -81,23 +108,23 @@ struct DiagCursor {
     }
 };
 
-// diagonals staged ahead of the dependent chain (power of two); fewer when a thread owns several columns, so that
-// the ring of a 1024-thread CTA stays at 128 KB
-template <int C>
-struct Ring {
-    static constexpr int depth = C == 1 ? 8 : (C == 2 ? 4 : 2);
-};
+// R = diagonals staged ahead of the dependent chain (power of two: 8, 4 or 2, the deepest whose ring fits in shared
+// memory for the CTA's thread count). C = columns per thread: 1 up to 1024 columns, 4 up to 2048, 8 up to 4096.
+// One column per thread is the fast shape: a warp issues roughly one instruction every four cycles on this chain, so
+// the time of a step follows the instruction count of one warp, and spreading columns over more warps (which run on
+// the SM's four schedulers side by side) beats giving a thread several columns (measured: 3 columns per thread in a
+// single warp took 148 us where 3 warps take 80 us on the same 81-column lattices).
 
-// One direction of one sequence. `stage` is dynamic shared memory: 2 * Ring<C>::depth * C * blockDim.x doubles; each thread
+// One direction of one sequence. `stage` is dynamic shared memory: 2 * R * C * blockDim.x doubles; each thread
 // stages the operands of its own columns with 8-byte cp.async copies (no register scoreboard is held while they are
 // in flight, unlike plain loads) and reads them back one step ahead of use.
-template <int C, bool F64, bool BETA>
+template <int C, int R, bool F64, bool BETA>
 __device__ __forceinline__ void run_direction(int T, int U, const double *__restrict__ lpb,
                                               const double *__restrict__ lpl, double *__restrict__ out,
                                               double *__restrict__ ll_out, int n_active, double (*edge)[32],
-                                              double *stage)
+                                              double *stage, const float4 *__restrict__ lse_tab)
 {
-    constexpr int kRing = Ring<C>::depth;
+    constexpr int kRing = R;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n_warps = n_active >> 5;
     const int m = U + 1;
@@ -118,22 +145,29 @@ __device__ __forceinline__ void run_direction(int T, int U, const double *__rest
         pf.base = T * m - 1 - U;  // the last diagonal holds the single cell (T-1, U)
     }
 
-    // stage the operands of data diagonal pf.e into ring slot k
+    // Stage the operands of data diagonal pf.e into ring slot k. An operand that does not exist (cell outside the
+    // lattice, no label move out of the last column, ...) is staged as 0.0: the recursion below is branch-free and
+    // relies on absent moves meeting a -inf running value, so their operand only has to be finite.
+    // sbase[k] = base of the data diagonal staged in slot k. The results go out diagonal-major as well, and the
+    // diagonal a step writes is one whose base is already here: beta writes the diagonal it reads (slot k), alpha
+    // writes the diagonal the next step reads (slot k+1).
+    int sbase[kRing];
     auto issue = [&](int k) {
+        sbase[k] = pf.base;
 #pragma unroll
         for (int j = 0; j < C; ++j) {
             const int u = u0 + j;
             const int tb = pf.e - u;
+            double *sb = st_b + (k * C + j) * nt, *sl = st_l + (k * C + j) * nt;
             if (!BETA) {
                 // step e+1 at column u needs blank(e-u, u) and label(e-u+1, u-1)
-                if (u <= U && tb >= 0 && tb <= T - 2) cp_async8(st_b + (k * C + j) * nt, lpb + pf.base + u);
-                if (u <= U && u >= 1 && tb >= -1 && tb <= T - 2) cp_async8(st_l + (k * C + j) * nt, lpl + pf.base + u - 1);
+                if (u <= U && tb >= 0 && tb <= T - 2) cp_async8(sb, lpb + pf.base + u); else *sb = 0.0;
+                if (u <= U && u >= 1 && tb >= -1 && tb <= T - 2) cp_async8(sl, lpl + pf.base + u - 1); else *sl = 0.0;
             } else {
                 // step with d = e at column u needs blank(e-u, u) and label(e-u, u)
-                if (u <= U && tb >= 0 && tb <= T - 1) {
-                    cp_async8(st_b + (k * C + j) * nt, lpb + pf.base + u);
-                    if (u < U) cp_async8(st_l + (k * C + j) * nt, lpl + pf.base + u);
-                }
+                const bool cell = u <= U && tb >= 0 && tb <= T - 1;
+                if (cell) cp_async8(sb, lpb + pf.base + u); else *sb = 0.0;
+                if (cell && u < U) cp_async8(sl, lpl + pf.base + u); else *sl = 0.0;
             }
         }
         cp_async_commit();
@@ -143,24 +177,33 @@ __device__ __forceinline__ void run_direction(int T, int U, const double *__rest
 #pragma unroll
     for (int k = 0; k < kRing; ++k) issue(k);
 
+    // Running values. Cells outside the lattice count as -inf, which makes every boundary case fall out of the one
+    // interior formula v = LSE(own + blank, neighbour + label):
+    //   alpha: column u starts at -inf (virtual row t = -1), column 0 starts at 0 with a zero operand so that
+    //          alpha(0,0) = LSE(0 + 0, -inf) = 0; the left neighbour of column 0 is -inf.
+    //   beta : column u starts at -inf (virtual row t = T), column U starts at 0 so that
+    //          beta(T-1,U) = LSE(0 + blank(T-1,U), -inf); columns beyond U stay -inf for ever.
     double cur_b[C], cur_l[C], nxt_b[C], nxt_l[C], prev[C];
+    int tcur[C];  // frame index of column j at the current step; parked far outside [0,T) for columns beyond U
     cp_async_wait<kRing - 1>();
 #pragma unroll
     for (int j = 0; j < C; ++j) {
+        const int u = u0 + j;
         cur_b[j] = st_b[j * nt];
         cur_l[j] = st_l[j * nt];
-        prev[j] = 0.0;
+        prev[j] = (u == (BETA ? U : 0)) ? 0.0 : -INFINITY;
+        tcur[j] = u <= U ? (BETA ? nd - 1 - u : -u) : INT_MIN / 2;
     }
+    const bool no_neighbour = BETA ? (u0 + C - 1 >= U) : (tid == 0);
 
-    // row-major cell index (relative to the sequence) of column u0 at the current step; +-m per step
-    int64_t cell0 = BETA ? int64_t(nd - 1 - u0) * m + u0 : int64_t(0 - u0) * m + u0;
 
     for (int s0 = 0; s0 < nd; s0 += kRing) {
 #pragma unroll
         for (int k = 0; k < kRing; ++k) {
             const int s = s0 + k;
             if (s >= nd) break;
-            const int d = BETA ? nd - 1 - s : s;
+
+            const int out_base = sbase[BETA ? k : (k + 1) % kRing];  // before issue(k) recycles the slot
 
             // operands of the next step out of the ring, then refill the slot this step's operands came from
             cp_async_wait<kRing - 2>();
@@ -177,34 +220,30 @@ __device__ __forceinline__ void run_direction(int T, int U, const double *__rest
                 if (!BETA && lane == 0 && warp > 0) nb = edge[(s + 1) & 1][warp - 1];
                 if (BETA && lane == 31 && warp + 1 < n_warps) nb = edge[(s + 1) & 1][warp + 1];
             }
+            if (no_neighbour) nb = -INFINITY;
+            // step 0 starts from the virtual row: its 0 at the start column must not reach the neighbouring column
+            const bool first = (k == 0) && (s0 == 0);
 
             double nw[C];
 #pragma unroll
             for (int j = 0; j < C; ++j) {
-                const int u = u0 + j;
-                const int t = d - u;
-                const bool active = (u <= U) && (t >= 0) && (t <= T - 1);
-                const bool has_skip = active && (BETA ? t < T - 1 : t >= 1);
-                const bool has_emit = active && (BETA ? u < U : u >= 1);
                 double other;  // neighbour column operand
                 if (!BETA)
                     other = (j == 0) ? nb : prev[j - 1];
                 else
                     other = (j == C - 1) ? nb : prev[j + 1];
-                const double skip = has_skip ? prev[j] + cur_b[j] : -INFINITY;
-                const double emit = has_emit ? other + cur_l[j] : -INFINITY;
-                double v = lse2<F64>(skip, emit);
-                if (!has_skip && !has_emit) v = BETA ? cur_b[j] : 0.0;  // beta(T-1,U) = blank(T-1,U); alpha(0,0) = 0
+                if (first) other = -INFINITY;
+                const double v = lse2<F64>(prev[j] + cur_b[j], other + cur_l[j], lse_tab);
                 nw[j] = v;
-                if (active) out[cell0 + int64_t(j) * (1 - m)] = v;
+                if (unsigned(tcur[j]) < unsigned(T)) out[out_base + u0 + j] = v;
             }
 #pragma unroll
             for (int j = 0; j < C; ++j) {
                 prev[j] = nw[j];
                 cur_b[j] = nxt_b[j];
                 cur_l[j] = nxt_l[j];
+                tcur[j] += BETA ? -1 : 1;
             }
-            cell0 += BETA ? -m : m;
 
             if (n_warps > 1) {
                 if (!BETA && lane == 31) edge[s & 1][warp] = prev[C - 1];
@@ -229,48 +268,51 @@ __device__ __forceinline__ void run_direction(int T, int U, const double *__rest
     }
 }
 
-template <int C, bool F64>
-__global__ void __launch_bounds__(1024)
-wavefront_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int B, int flags, int mean_den,
-                 int n_dirs, Workspace w, typename std::conditional<F64, double, float>::type *__restrict__ costs,
-                 typename std::conditional<F64, double, float>::type *__restrict__ loss)
+// Thread budget per CTA: one column per thread up to 1024 columns; C = 4 and 8 cover up to 2048 and 4096 columns with
+// at most 512 threads, which leaves 128 registers per thread for the C recursions of a thread.
+template <int C>
+struct MaxThreads {
+    static constexpr int value = C == 1 ? 1024 : 512;
+};
+
+// Everything a wavefront CTA needs besides its shared memory.
+template <typename CostT>
+struct WaveArgs {
+    const int32_t *lx, *ly;
+    int B, flags, mean_den, n_dirs;
+    Workspace w;
+    CostT *costs, *loss;
+    // sharded runs: costs are also written into their global slots of a [n_global + 1] vector (the partial loss goes
+    // into the last slot, every other slot is zeroed), ready for one all-reduce(sum) across ranks
+    const int32_t *global_ids;
+    int n_global;
+    CostT *cost_vec;
+};
+
+// Completion ticket: the last CTA of the grid turns the per-sequence log-likelihoods into costs, status and loss.
+template <typename CostT>
+__device__ __forceinline__ void finalize_if_last(const WaveArgs<CostT> &g, int n_active, double (*edge)[32],
+                                                 int *last_flag)
 {
-    using CostT = typename std::conditional<F64, double, float>::type;
-    extern __shared__ double stage[];
-    __shared__ double edge[2][32];
-    __shared__ int last_flag;
-    if (w.status[0] & CWRNNT_ST_FATAL) return;
-
-    const int n = w.order[blockIdx.x / n_dirs];
-    const bool beta_dir = (n_dirs == 1) || (blockIdx.x & 1);
-    const int T = lx[n], U = ly[n];
-    const int64_t off = w.off[n];
-    const int cols = (U + 1 + C - 1) / C;
-    const int n_active = min(int(blockDim.x), (cols + 31) & ~31);
-    if (int(threadIdx.x) >= n_active) return;  // whole warps leave; the rest synchronise on a named barrier
-
-    if (beta_dir)
-        run_direction<C, F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n, n_active,
-                                    edge, stage);
-    else
-        run_direction<C, F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off, w.ll_alpha + n,
-                                     n_active, edge, stage);
-
-    // ---- completion ticket: the last CTA of the grid finalises costs, status and loss
+    const Workspace &w = g.w;
     __threadfence();
     cta_sync(n_active);
     if (threadIdx.x == 0) {
         const unsigned int t = atomicAdd(w.ticket, 1u);
-        last_flag = (t == gridDim.x - 1);
+        *last_flag = (t == gridDim.x - 1);
     }
     cta_sync(n_active);
-    if (!last_flag) return;
+    if (!*last_flag) return;
     __threadfence();
 
+    if (g.cost_vec)
+        for (int i = threadIdx.x; i <= g.n_global; i += n_active) g.cost_vec[i] = CostT(0);
+    cta_sync(n_active);
+
     double partial = 0.0;
-    for (int i = threadIdx.x; i < B; i += n_active) {
+    for (int i = threadIdx.x; i < g.B; i += n_active) {
         double b = __ldcg(w.ll_beta + i);
-        if (n_dirs == 2) {
+        if (g.n_dirs == 2) {
             // forward/backward consistency guard of the reference (cwarp_cuda_rnnt_kernel.cu:350-366)
             const double a = __ldcg(w.ll_alpha + i);
             const double big = fmax(a, b);
@@ -279,11 +321,12 @@ wavefront_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly,
                 atomicOr(w.status, CWRNNT_ST_FWD_BWD_GAP);
             }
         }
-        const double c = -b * sequence_scale(flags, lx[i]);
-        costs[i] = CostT(c);
+        const double c = -b * sequence_scale(g.flags, g.lx[i]);
+        g.costs[i] = CostT(c);
+        if (g.cost_vec) g.cost_vec[g.global_ids ? g.global_ids[i] : i] = CostT(c);
         partial += c;
     }
-    if (flags & (CWRNNT_REDUCE_MEAN | CWRNNT_REDUCE_SUM)) {
+    if ((g.flags & (CWRNNT_REDUCE_MEAN | CWRNNT_REDUCE_SUM)) || g.cost_vec) {
         // fixed-order block sum: lanes, then warps
 #pragma unroll
         for (int sft = 16; sft > 0; sft >>= 1) partial += __shfl_xor_sync(0xffffffffu, partial, sft);
@@ -293,66 +336,111 @@ wavefront_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly,
         if (threadIdx.x == 0) {
             double tot = 0.0;
             for (int k = 0; k < (n_active >> 5); ++k) tot += edge[0][k];
-            if (flags & CWRNNT_REDUCE_MEAN) tot /= double(mean_den > 0 ? mean_den : B);
-            if (loss) *loss = CostT(tot);
+            if (g.flags & CWRNNT_REDUCE_MEAN) tot /= double(g.mean_den > 0 ? g.mean_den : g.B);
+            if (g.loss) *g.loss = CostT(tot);
+            if (g.cost_vec) g.cost_vec[g.n_global] = CostT(tot);
         }
     }
     if (threadIdx.x == 0) *w.ticket = 0u;
 }
 
+// Generic path: C columns per thread, per-thread cp.async ring of depth R.
+template <int C, int R, bool F64>
+__global__ void __launch_bounds__(MaxThreads<C>::value)
+wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g)
+{
+    extern __shared__ __align__(16) double stage[];
+    __shared__ double edge[2][32];
+    __shared__ float4 lse_tab[F64 ? 1 : kLseNodes];
+    __shared__ int last_flag;
+    const Workspace &w = g.w;
+    if (w.status[0] & CWRNNT_ST_FATAL) return;
+
+    const int n = w.order[blockIdx.x / g.n_dirs];
+    const bool beta_dir = (g.n_dirs == 1) || (blockIdx.x & 1);
+    const int T = g.lx[n], U = g.ly[n];
+    const int64_t off = w.off[n];
+    const int cols = (U + 1 + C - 1) / C;
+    const int n_active = min(int(blockDim.x), (cols + 31) & ~31);
+    if (int(threadIdx.x) >= n_active) return;  // whole warps leave; the rest synchronise on a named barrier
+    if (!F64) {
+        build_lse_table(lse_tab, threadIdx.x, n_active);
+        cta_sync(n_active);
+    }
+    if (beta_dir)
+        run_direction<C, R, F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n, n_active,
+                                       edge, stage, lse_tab);
+    else
+        run_direction<C, R, F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off, w.ll_alpha + n,
+                                        n_active, edge, stage, lse_tab);
+    finalize_if_last(g, n_active, edge, &last_flag);
+}
+
+template <typename K>
+static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
+{
+    if (smem <= 32 * 1024) return cudaSuccess;  // default cap is 48 KB including ~9 KB of static arrays
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess)
+        std::fprintf(stderr, "cwrnnt: cannot opt in to %zu bytes of shared memory (%d threads): %s\n", smem, threads,
+                     cudaGetErrorString(e));
+    return e;
+}
+
 template <bool F64>
 static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                                      void *costs, void *loss, cudaStream_t s)
+                                      void *costs, void *loss, const ShardOutput *shard, cudaStream_t s)
 {
     using CostT = typename std::conditional<F64, double, float>::type;
     if (p.B == 0) return cudaSuccess;
-    const int n_dirs = (p.flags & CWRNNT_COSTS_ONLY) ? 1 : 2;
+    WaveArgs<CostT> g{};
+    g.lx = lx;
+    g.ly = ly;
+    g.B = p.B;
+    g.flags = p.flags;
+    g.mean_den = p.mean_denominator;
+    g.n_dirs = (p.flags & CWRNNT_COSTS_ONLY) ? 1 : 2;
+    g.w = w;
+    g.costs = static_cast<CostT *>(costs);
+    g.loss = static_cast<CostT *>(loss);
+    if (shard && shard->cost_vector) {
+        g.global_ids = shard->global_ids;
+        g.n_global = shard->n_global;
+        g.cost_vec = static_cast<CostT *>(shard->cost_vector);
+    }
     const int cols = p.max_u + 1;
-    const int C = cols <= 1024 ? 1 : (cols <= 2048 ? 2 : 4);
+    const int grid = p.B * g.n_dirs;
+    cudaError_t e = cudaSuccess;
+
+    const int C = cols <= 1024 ? 1 : (cols <= 2048 ? 4 : 8);
     const int per_thread_cols = (cols + C - 1) / C;
     const int threads = (per_thread_cols + 31) & ~31;
-    const int grid = p.B * n_dirs;
-    CostT *c = static_cast<CostT *>(costs);
-    CostT *l = static_cast<CostT *>(loss);
-    cudaError_t e = cudaSuccess;
-#define CWRNNT_LAUNCH_WAVEFRONT(CC)                                                                               \
-    {                                                                                                             \
-        const size_t smem = size_t(2) * Ring<CC>::depth * CC * threads * sizeof(double);                          \
-        if (smem > 40 * 1024) { /* default cap is 48 KB including the static part: opt in above 40 KB */       \
-            e = cudaFuncSetAttribute(wavefront_kernel<CC, F64>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
-                                     int(smem));                                                                  \
-            if (e != cudaSuccess) {                                                                               \
-                std::fprintf(stderr, "cwrnnt: cannot opt in to %zu bytes of shared memory (%d threads): %s\n",    \
-                             smem, threads, cudaGetErrorString(e));                                               \
-                return e;                                                                                         \
-            }                                                                                                     \
-        }                                                                                                         \
-        wavefront_kernel<CC, F64><<<grid, threads, smem, s>>>(lx, ly, p.B, p.flags, p.mean_denominator, n_dirs,   \
-                                                              w, c, l);                                           \
-        e = cudaGetLastError();                                                                                   \
-        if (e != cudaSuccess) {                                                                                   \
-            cudaFuncAttributes fa{};                                                                              \
-            cudaFuncGetAttributes(&fa, wavefront_kernel<CC, F64>);                                                \
-            std::fprintf(stderr,                                                                                  \
-                         "cwrnnt: wavefront launch failed (%s): grid %d, block %d, dynamic smem %zu; kernel: "     \
-                         "%d regs, %zu static smem, max dynamic %d, max threads %d\n",                            \
-                         cudaGetErrorString(e), grid, threads, smem, fa.numRegs, fa.sharedSizeBytes,              \
-                         fa.maxDynamicSharedSizeBytes, fa.maxThreadsPerBlock);                                    \
-            return e;                                                                                             \
-        }                                                                                                         \
+    const int R = C == 1 ? 8 : (threads * C <= 1280 ? 8 : (threads * C <= 2560 ? 4 : 2));  // deepest ring <= 160 KB
+    const size_t smem = size_t(2) * R * C * threads * sizeof(double);
+#define CWRNNT_LAUNCH_WAVEFRONT(CC, RR)                                                      \
+    {                                                                                        \
+        if ((e = opt_in_smem(wavefront_kernel<CC, RR, F64>, smem, threads)) != cudaSuccess) return e; \
+        wavefront_kernel<CC, RR, F64><<<grid, threads, smem, s>>>(g);                        \
     }
-    if (C == 1) CWRNNT_LAUNCH_WAVEFRONT(1)
-    else if (C == 2) CWRNNT_LAUNCH_WAVEFRONT(2)
-    else CWRNNT_LAUNCH_WAVEFRONT(4)
+#define CWRNNT_PICK_RING(CC)                                   \
+    {                                                          \
+        if (R == 8) CWRNNT_LAUNCH_WAVEFRONT(CC, 8)             \
+        else if (R == 4) CWRNNT_LAUNCH_WAVEFRONT(CC, 4)        \
+        else CWRNNT_LAUNCH_WAVEFRONT(CC, 2)                    \
+    }
+    if (C == 1) CWRNNT_LAUNCH_WAVEFRONT(1, 8)
+    else if (C == 4) CWRNNT_PICK_RING(4)
+    else CWRNNT_PICK_RING(8)
+#undef CWRNNT_PICK_RING
 #undef CWRNNT_LAUNCH_WAVEFRONT
     return cudaGetLastError();
 }
 
 cudaError_t launch_wavefront(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                             void *costs, void *loss, cudaStream_t s)
+                             void *costs, void *loss, const ShardOutput *shard, cudaStream_t s)
 {
-    return p.dtype == CWRNNT_F64 ? launch_wavefront_t<true>(p, lx, ly, w, costs, loss, s)
-                                 : launch_wavefront_t<false>(p, lx, ly, w, costs, loss, s);
+    return p.dtype == CWRNNT_F64 ? launch_wavefront_t<true>(p, lx, ly, w, costs, loss, shard, s)
+                                 : launch_wavefront_t<false>(p, lx, ly, w, costs, loss, shard, s);
 }
 
 }  // namespace cwrnnt

@@ -110,6 +110,20 @@ CWRNNT_API int cwrnnt_forward(const cwrnnt_problem *p, const void *x, const int3
                    void *workspace, int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream);
 
 /*
+ * Forward of one shard of a batch that is split across GPUs by whole sequences (one process per GPU). As
+ * cwrnnt_forward, and in addition the kernel's epilogue fills `cost_vector` [n_global + 1] (costs type): zero
+ * everywhere except cost_vector[global_ids[n]] = costs[n] for this rank's sequences and cost_vector[n_global] = this
+ * rank's loss contribution (sum of its costs, divided by mean_denominator under CWRNNT_REDUCE_MEAN). One
+ * all-reduce(sum) of that vector over the ranks then leaves every sequence's cost and the global loss on every rank.
+ * global_ids NULL means the identity. No counterpart in the reference, which is single-GPU (no device guard, no
+ * collective anywhere in its tree).
+ */
+CWRNNT_API int cwrnnt_forward_sharded(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly,
+                                      const int32_t *y, void *workspace, int64_t workspace_bytes, void *costs,
+                                      void *loss, const int32_t *global_ids, int32_t n_global, void *cost_vector,
+                                      cwrnnt_stream_t stream);
+
+/*
  * Backward: grad_x[r][k] = d (sum_n g_n * costs[n]) / d x[r][k] in one streaming pass over [n_rows, V].
  * Replaces compact_rnnt_loss_backward_ (cwarp_cuda.cpp:110-136 = cwarp_cuda_backward_ + zeros[STU,V] +
  * gather_cuda_backward_) and, with CWRNNT_FUSED_LOG_SOFTMAX, the caller's log_softmax backward as well.

@@ -221,6 +221,38 @@ def test_benchmark_shapes_properties(oracle, cfg):
     assert np.abs(got["grad"].sum(-1)).max() < (1e-4 if dtype == torch.float32 else 2e-2)
 
 
+def test_sharded_forward_fills_global_cost_vector(oracle):
+    """Two shards of one batch, run one after the other on one GPU: each fills its own slots of the cost vector and
+    zeroes the rest, so the sum of the two vectors (what the all-reduce computes) is every cost plus the mean loss."""
+    from compactwarprnntloss_b200 import capi, sharding
+    case = ragged_case(71, 7, (3, 25), (1, 9), V=32)
+    costs64, _ = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, want_grad=False)
+    plan = sharding.plan_shards(case["lx"], case["ly"], 2)
+    off = np.concatenate([[0], np.cumsum(case["lx"].astype(np.int64) * (case["ly"] + 1))])
+    total = torch.zeros(8, device="cuda:0")
+    for ids in plan:
+        rows = np.concatenate([np.arange(off[i], off[i + 1]) for i in ids])
+        x = torch.as_tensor(case["x"][rows]).cuda().contiguous()
+        lx = torch.as_tensor(case["lx"][ids]).cuda()
+        ly = torch.as_tensor(case["ly"][ids]).cuda()
+        y = torch.as_tensor(case["y"][ids]).cuda().contiguous()
+        p = capi.make_problem(x, lx, y, 0, capi.FUSED_LOG_SOFTMAX | capi.REDUCE_MEAN, mean_denominator=7)
+        ws = capi.alloc_workspace(p, x.device)
+        costs = torch.empty(len(ids), device="cuda:0")
+        loss = torch.empty((), device="cuda:0")
+        vec = torch.full((8,), float("nan"), device="cuda:0")
+        capi.forward_sharded(p, x, lx, ly, y, ws, costs, loss, torch.tensor(ids, dtype=torch.int32, device="cuda:0"),
+                             7, vec)
+        v = vec.cpu().numpy()
+        others = [i for i in range(7) if i not in ids]
+        assert np.all(v[others] == 0.0)
+        np.testing.assert_allclose(v[ids], costs.cpu().numpy(), rtol=0)
+        assert abs(v[7] - float(loss)) == 0.0
+        total += vec
+    np.testing.assert_allclose(total[:7].cpu().numpy(), costs64, rtol=LOSS_RTOL)
+    assert abs(float(total[7]) - costs64.mean()) <= LOSS_RTOL * costs64.mean()
+
+
 def test_host_pipeline_matches_device_path(oracle):
     from compactwarprnntloss_b200 import capi
     from tests.gpu_helpers import run_engine
