@@ -376,6 +376,156 @@ wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g
     finalize_if_last(g, n_active, edge, &last_flag);
 }
 
+// ------------------------------------------------------------------------------------------------ split-role path
+// Up to 512 columns. The time of a step follows the number of instructions one warp has to issue on it (a warp on this
+// chain issues about one instruction every four to five cycles and no other warp of the sequence can take its place),
+// so the work of a 32-column group is split over two warps that run side by side on the SM's schedulers:
+//   compute warp: operands out of the shared-memory ring, neighbour value, the log-sum-exp, result into shared memory;
+//   helper warp : stages the operands `R` steps ahead (8-byte cp.async, all the index arithmetic and predicates),
+//                 and moves the previous step's results from shared memory to global memory.
+// Results pass through a double-buffered row `vbuf[2][columns]`, which also serves as the neighbour exchange (no
+// shuffles, no warp-seam special case). One named barrier per step joins all warps of the CTA.
+// Hand-over of ring slot x % R (operands of step x): the helper's copy group for step s+2 is complete before the
+// barrier that ends step s; the compute warp reads the operands of step s+1 during step s (one step ahead, into
+// registers); the helper refills slot s % R during step s, after its last read during step s-1.
+template <int R, bool F64, bool BETA>
+__device__ __forceinline__ void run_direction_split(int T, int U, const double *__restrict__ lpb,
+                                                    const double *__restrict__ lpl, double *__restrict__ out,
+                                                    double *__restrict__ ll_out, int n_cols, int n_sync,
+                                                    double *stage, double *vbuf,
+                                                    const float4 *__restrict__ lse_tab, bool helper, int u)
+{
+    const int m = U + 1;
+    const int nd = T + U;
+    double *st_b = stage + u;                    // slot k at st_b[k * n_cols]
+    double *st_l = stage + R * n_cols + u;
+    double *v0 = vbuf, *v1 = vbuf + n_cols;      // results of even / odd steps
+
+    if (helper) {
+        DiagCursor pf;
+        pf.T = T;
+        pf.U = U;
+        if (!BETA) {
+            pf.e = -1;
+            pf.base = 0;
+        } else {
+            pf.e = nd - 1;
+            pf.base = T * m - 1 - U;
+        }
+        int sbase[R];
+        auto issue = [&](int k) {
+            sbase[k] = pf.base;
+            const int tb = pf.e - u;
+            double *sb = st_b + k * n_cols, *sl = st_l + k * n_cols;
+            if (!BETA) {
+                if (u <= U && tb >= 0 && tb <= T - 2) cp_async8(sb, lpb + pf.base + u); else *sb = 0.0;
+                if (u <= U && u >= 1 && tb >= -1 && tb <= T - 2) cp_async8(sl, lpl + pf.base + u - 1); else *sl = 0.0;
+            } else {
+                const bool cell = u <= U && tb >= 0 && tb <= T - 1;
+                if (cell) cp_async8(sb, lpb + pf.base + u); else *sb = 0.0;
+                if (cell && u < U) cp_async8(sl, lpl + pf.base + u); else *sl = 0.0;
+            }
+            cp_async_commit();
+            if (!BETA) pf.up(); else pf.down();
+        };
+#pragma unroll
+        for (int k = 0; k < R; ++k) issue(k);
+        cp_async_wait<R - 2>();  // operands of steps 0 and 1 are in place
+        int tprev = u <= U ? (BETA ? nd - u : -u - 1) : INT_MIN / 2;  // frame index of this column one step ago
+        int last_base = 0;
+        asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");      // start barrier
+
+        // step s: store the result of step s-1, refill slot s % R with the operands of step s+R
+        for (int s0 = 0; s0 <= nd; s0 += R) {
+#pragma unroll
+            for (int k = 0; k < R; ++k) {
+                const int s = s0 + k;
+                if (s > nd) break;
+                // diagonal written by step s-1: alpha -> the data diagonal of step s (slot k, read before issue(k)
+                // recycles it); beta -> the data diagonal of step s-1 (remembered from the previous round)
+                const int this_base = sbase[k];
+                const int out_base = BETA ? last_base : this_base;
+                last_base = this_base;
+                if (s >= 1 && unsigned(tprev) < unsigned(T)) out[out_base + u] = ((s - 1) & 1) ? v1[u] : v0[u];
+                tprev += BETA ? -1 : 1;
+                if (s == nd) break;  // last round only drains the final result
+                issue(k);
+                cp_async_wait<R - 2>();
+                asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+            }
+        }
+        cp_async_wait<0>();
+        return;
+    }
+
+    // ---- compute warp
+    double prev = (u == (BETA ? U : 0)) ? 0.0 : -INFINITY;
+    const bool no_neighbour = BETA ? (u >= U) : (u == 0);
+    const int nb_col = BETA ? min(u + 1, n_cols - 1) : max(u - 1, 0);
+    asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");  // start barrier: operands of steps 0 and 1 are staged
+    double cur_b = st_b[0], cur_l = st_l[0];
+    for (int s0 = 0; s0 < nd; s0 += R) {
+#pragma unroll
+        for (int k = 0; k < R; ++k) {
+            const int s = s0 + k;
+            if (s >= nd) break;
+            const double nxt_b = st_b[((k + 1) % R) * n_cols];
+            const double nxt_l = st_l[((k + 1) % R) * n_cols];
+            double nb = (s & 1) ? v0[nb_col] : v1[nb_col];  // the neighbour's result of step s-1
+            if (no_neighbour || s == 0) nb = -INFINITY;      // step 0 starts from the virtual row
+            const double v = lse2<F64>(prev + cur_b, nb + cur_l, lse_tab);
+            if (s & 1) v1[u] = v; else v0[u] = v;
+            prev = v;
+            cur_b = nxt_b;
+            cur_l = nxt_l;
+            asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+        }
+    }
+    if (!BETA) {
+        if (u == U) *ll_out = prev + __ldg(lpb + int64_t(T) * m - 1);
+    } else {
+        if (u == 0) *ll_out = prev;
+    }
+}
+
+template <int R, bool F64>
+__global__ void __launch_bounds__(1024)
+wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g)
+{
+    extern __shared__ __align__(16) double stage[];
+    __shared__ double edge[2][32];
+    __shared__ float4 lse_tab[F64 ? 1 : kLseNodes];
+    __shared__ int last_flag;
+    const Workspace &w = g.w;
+    if (w.status[0] & CWRNNT_ST_FATAL) return;
+
+    const int n = w.order[blockIdx.x / g.n_dirs];
+    const bool beta_dir = (g.n_dirs == 1) || (blockIdx.x & 1);
+    const int T = g.lx[n], U = g.ly[n];
+    const int64_t off = w.off[n];
+    const int half = blockDim.x >> 1;                 // compute threads launched (then as many helpers)
+    const int n_cols = min(half, (U + 1 + 31) & ~31);  // columns padded to whole warps for this sequence
+    // threads [0, n_cols) compute, [half, half + n_cols) help; the others leave (whole warps)
+    const int tid = threadIdx.x;
+    const bool is_helper = tid >= half;
+    const int col = is_helper ? tid - half : tid;
+    if (col >= n_cols) return;
+    const int n_sync = 2 * n_cols;
+    const int vtid = is_helper ? n_cols + col : col;  // dense numbering of the threads that stay
+    if (!F64) build_lse_table(lse_tab, vtid, n_sync);
+    asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+    double *vbuf = stage + 2 * R * n_cols;
+    if (beta_dir)
+        run_direction_split<R, F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n,
+                                          n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+    else
+        run_direction_split<R, F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off, w.ll_alpha + n,
+                                           n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+    // the compute warps finalise (helpers are done; n_cols threads with dense ids 0..n_cols-1)
+    if (is_helper) return;
+    finalize_if_last(g, n_cols, edge, &last_flag);
+}
+
 template <typename K>
 static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
 {
@@ -412,6 +562,16 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
     const int grid = p.B * g.n_dirs;
     cudaError_t e = cudaSuccess;
 
+    if (cols <= 512) {
+        // split-role path: one compute and one helper thread per column
+        constexpr int R = 8;
+        const int half = (cols + 31) & ~31;
+        const int threads = 2 * half;
+        const size_t smem = size_t(2 * R + 2) * half * sizeof(double);
+        if ((e = opt_in_smem(wavefront_split_kernel<R, F64>, smem, threads)) != cudaSuccess) return e;
+        wavefront_split_kernel<R, F64><<<grid, threads, smem, s>>>(g);
+        return cudaGetLastError();
+    }
     const int C = cols <= 1024 ? 1 : (cols <= 2048 ? 4 : 8);
     const int per_thread_cols = (cols + C - 1) / C;
     const int threads = (per_thread_cols + 31) & ~31;
