@@ -327,7 +327,7 @@ def main():
                    "l2": "inputs larger than L2 (no flush needed)", "reduction": wl.reduction,
                    "shard_imbalance": round(sharding.shard_imbalance(lx, ly, plan), 4)},
         "gpu_launches": 4 * K,
-        "kernels_per_step": ["prep_kernel", "gather_rows_kernel", "wavefront_kernel", "grad_rows_kernel"],
+        "kernels_per_step": ["prep_kernel", "gather_rows_kernel", "wavefront_split_kernel", "grad_rows_kernel"],
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "loss": loss_value,
         "roofline": {"bound": "hbm", "kernel": "grad_rows_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",

@@ -269,3 +269,43 @@ def test_host_pipeline_matches_device_path(oracle):
     np.testing.assert_allclose(costs.numpy(), dev["costs"], rtol=1e-6)
     assert abs(float(loss) - dev["loss"]) < 1e-5 * abs(dev["loss"])
     assert np.abs(gx.numpy() - dev["grad"]).max() < 1e-7
+
+
+def test_more_than_2_31_elements_bf16(oracle):
+    """V=4096 bfloat16, 2.2 G elements (the reference's 32-bit accessors reject such a tensor): row offsets and element
+    indices are 64-bit. The first and the last sequence (whose rows lie beyond element 2^31) are checked against the
+    oracle; the rest through the zero row-sum property of the logit gradient."""
+    from compactwarprnntloss_b200 import capi
+    dev = torch.device("cuda:0")
+    V, B = 4096, 12
+    rng = np.random.default_rng(5)
+    lx = rng.integers(300, 501, size=B).astype(np.int32)
+    ly = rng.integers(100, 151, size=B).astype(np.int32)
+    rows = int((lx.astype(np.int64) * (ly + 1)).sum())
+    while rows * V <= 2 ** 31 + 2 ** 27:
+        lx = lx + 20
+        rows = int((lx.astype(np.int64) * (ly + 1)).sum())
+    y = rng.integers(1, V, size=(B, int(ly.max()))).astype(np.int32)
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = (torch.randn(rows, V, device=dev, generator=g) * 3.0).to(torch.bfloat16)
+    lxd, lyd, yd = torch.tensor(lx, device=dev), torch.tensor(ly, device=dev), torch.tensor(y, device=dev)
+    p = capi.make_problem(x, lxd, yd, 0, capi.FUSED_LOG_SOFTMAX | capi.REDUCE_SUM)
+    ws = capi.alloc_workspace(p, dev)
+    costs = torch.empty(B, device=dev)
+    loss = torch.empty((), device=dev)
+    gx = torch.empty_like(x)
+    capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
+    capi.backward(p, x, lxd, lyd, yd, ws, None, 0, gx)
+    assert capi.read_status(ws)[0] == 0
+    off = np.concatenate([[0], np.cumsum(lx.astype(np.int64) * (ly + 1))])
+    assert off[-1] * V > 2 ** 31
+    for n in (0, B - 1):
+        xs = x[off[n]:off[n + 1]].double().cpu().numpy()
+        c64, d64 = oracle.fused(xs, lx[n:n + 1], ly[n:n + 1], y[n:n + 1], 0)
+        assert abs(float(costs[n]) - c64[0]) <= LOSS_RTOL * c64[0]
+        got = gx[off[n]:off[n + 1]].double().cpu().numpy()
+        assert np.abs(got - d64).max() <= GRAD_ATOL + 2.0 ** -8 * np.abs(d64).max()
+    assert abs(float(loss) - float(costs.double().sum())) <= 1e-5 * float(loss)
+    # every row of the logit gradient sums to ~0 (bf16 rounding of 4096 terms), sampled across the whole tensor
+    idx = torch.linspace(0, rows - 1, 4096, device=dev).long()
+    assert gx[idx].double().sum(-1).abs().max().item() < 0.05
