@@ -45,7 +45,7 @@ GRAD_KERNEL_DRAM_BYTES_PER_NODE = {2: 8039.0}
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cfg", type=int, default=2, help="workload (1-5); the headline metric is quoted on 2")
@@ -65,48 +65,86 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons of one GPU, sampled every 100 ms while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons of one GPU, polled through NVML (read-only queries) from a thread every
+    few milliseconds while the timed region runs; falls back to `nvidia-smi -lms` when NVML is unavailable."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
-    def __init__(self, device_index):
-        self.rows, self.proc = [], None
+    def __init__(self, device_index, period_s=0.003):
+        self.rows, self.stop_flag, self.mode, self.proc = [], False, None, None
+        self.period = period_s
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+            self.sm_max = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.mode = "nvml"
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self._start_smi(device_index)
+
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                try:
+                    why = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:  # noqa: BLE001
+                    why = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                self.rows.append((float(sm), int(why), pw))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(self.period)
+
+    def _start_smi(self, device_index):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
         try:
             uuid = str(torch.cuda.get_device_properties(device_index).uuid)
             sel = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", sel, "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", sel, "--query-gpu=" + q,
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.mode = "smi"
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except Exception:  # noqa: BLE001
-            self.proc = None
+            self.mode = None
 
-    def _read(self):
+    def _read_smi(self):
+        names = [0x8, 0x40, 0x20, 0x4]
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            c = [v.strip() for v in line.split(",")]
+            if len(c) >= 7 and c[0].replace(".", "").isdigit():
+                why = sum(bit for i, bit in enumerate(names) if c[3 + i].lower().startswith("active"))
+                self.sm_max = float(c[1])
+                self.rows.append((float(c[0]), why, float(c[2]) if c[2].replace(".", "").isdigit() else 0.0))
 
     def mark(self):
         return len(self.rows)
 
     def stop(self, start=0):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:  # noqa: BLE001
-            self.proc.kill()
-        rows = [r for r in self.rows[start:] if len(r) >= 7] or [r for r in self.rows if len(r) >= 7]
+        if self.mode is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML and no nvidia-smi"]}
+        if self.mode == "smi":
+            time.sleep(0.12)
+            self.proc.terminate()
+        self.stop_flag = True
+        rows = self.rows[start:] or self.rows[-1:]
         if not rows:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
-        sm = [float(r[0]) for r in rows if r[0].replace(".", "").isdigit()]
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": float(rows[0][1]),
-                "power_w_max": max(float(r[2]) for r in rows), "samples": len(rows), "reasons": reasons}
+        why = 0
+        for r in rows:
+            why |= r[1]
+        return {"sm_mhz": statistics.median(r[0] for r in rows), "sm_max_mhz": self.sm_max,
+                "power_w_max": max(r[2] for r in rows), "samples": len(rows), "source": self.mode,
+                "reasons": [n for bit, n in self.REASONS.items() if why & bit]}
 
 
 def host_threads():
