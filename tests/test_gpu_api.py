@@ -189,3 +189,35 @@ def test_live_reference_cuda_kernels_when_built(oracle):
     assert our_err <= 1e-5
     assert (a.grad - b.grad).abs().max().item() <= ref_err + 1e-5
     print(f"|ours-f64| {our_err:.2e}  |ref-f64| {ref_err:.2e}  |ours-ref| {(a.grad - b.grad).abs().max().item():.2e}")
+
+
+def test_forward_backward_capture_in_a_cuda_graph(oracle):
+    """The C-ABI calls allocate nothing and never synchronise, so a whole step can be captured once and replayed on
+    new data of the same shapes (lengths included, since they live on the device)."""
+    from compactwarprnntloss_b200 import capi
+    case = ragged_case(37, 6, (4, 30), (1, 12), V=64, sigma=1.5)
+    x, lx, y, ly = _tensors(case)
+    p = capi.make_problem(x, lx, y, 0, capi.FUSED_LOG_SOFTMAX | capi.REDUCE_MEAN)
+    ws = capi.alloc_workspace(p, x.device)
+    costs = torch.empty(6, device=DEV)
+    loss = torch.empty((), device=DEV)
+    gx = torch.empty_like(x)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        capi.forward(p, x, lx, ly, y, ws, costs, loss)   # first use outside capture (module load, smem opt-in)
+        capi.backward(p, x, lx, ly, y, ws, None, 0, gx)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            capi.forward(p, x, lx, ly, y, ws, costs, loss)
+            capi.backward(p, x, lx, ly, y, ws, None, 0, gx)
+    torch.cuda.synchronize()
+    for seed in (1, 2):
+        fresh = torch.randn(x.shape, generator=torch.Generator().manual_seed(seed)) * 1.5
+        x.copy_(fresh.to(DEV))
+        graph.replay()
+        torch.cuda.synchronize()
+        c64, d64 = oracle.fused(fresh.numpy(), case["lx"], case["ly"], case["y"], 0, weights=np.full(6, 1 / 6))
+        np.testing.assert_allclose(costs.cpu().numpy(), c64, rtol=1e-5)
+        assert abs(float(loss) - c64.mean()) <= 1e-5 * c64.mean()
+        assert np.abs(gx.cpu().numpy() - d64).max() <= 1e-5
