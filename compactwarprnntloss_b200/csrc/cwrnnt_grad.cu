@@ -45,13 +45,14 @@ __device__ __forceinline__ void row_terms(const RowWalker &rw, const Workspace &
 }
 
 // Same row shapes and row runs as the gather kernel. No warp-wide collective is needed here: each lane scales its own
-// part of the row by the row's occupancy sum.
-template <typename T, int LPR, int NV, bool FULL, bool RUNS>
+// part of the row by the row's occupancy sum. Plain (allocating) loads and stores: with the non-persistent grid the
+// evict-first variants measured 7 % slower.
+template <typename T, int LPR, int NV, bool FULL>
 __global__ void __launch_bounds__(kStreamThreads)
 grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_rows, int B,
                  const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, const int32_t *__restrict__ y,
                  int y_stride, int blank, int flags, double mean_inv, Workspace w,
-                 const typename Elt<T>::cost *__restrict__ grad_costs, int gc_stride)
+                 const typename Elt<T>::cost *__restrict__ grad_costs, int gc_stride, int run_len)
 {
     using E = Elt<T>;
     using A = typename E::acc;
@@ -62,20 +63,14 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_r
 
     const int gl = threadIdx.x % LPR;
     const int nvec = V / VE;
-    // RUNS: every lane group owns one contiguous run of rows; otherwise a CTA takes GPC consecutive rows per
-    // iteration and strides over the matrix by the grid size (fewer DRAM pages open at once).
-    const int64_t n_groups = int64_t(gridDim.x) * GPC;
-    const int64_t per_group = (n_rows + n_groups - 1) / n_groups;
-    const int64_t first = RUNS ? (int64_t(blockIdx.x) * GPC + threadIdx.x / LPR) * per_group
-                               : int64_t(blockIdx.x) * GPC + threadIdx.x / LPR;
-    const int64_t stride = RUNS ? 1 : n_groups;
-    const int64_t limit = RUNS ? (first + per_group < n_rows ? first + per_group : n_rows) : n_rows;
+    // A CTA covers GPC * run_len consecutive rows, one such tile per CTA (non-persistent grid, see the gather kernel).
+    const int64_t first = (int64_t(blockIdx.x) * GPC + threadIdx.x / LPR) * run_len;
+    const int64_t limit = first + run_len < n_rows ? first + run_len : n_rows;
     bool ignored = false;
 
     RowWalker rw;
-    for (int64_t r = first; r < limit; r += stride) {
+    for (int64_t r = first; r < limit; ++r) {
         if (r == first) rw.start(r, w.off, B, lx, ly);
-        else if (!RUNS) rw.restart(r, w.off, B, lx, ly);
         const T *row = x + r * int64_t(V);
         T *orow = gx + r * int64_t(V);
         const uint4 *rv = reinterpret_cast<const uint4 *>(row);
@@ -83,7 +78,7 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_r
         uint4 v[NV];
 #pragma unroll
         for (int j = 0; j < NV; ++j)
-            if (FULL || j * LPR + gl < nvec) v[j] = ld_stream(rv + j * LPR + gl);
+            if (FULL || j * LPR + gl < nvec) v[j] = ld_nc(rv + j * LPR + gl);
         const int label = rw.label(y, y_stride, V, ignored);
         const A xb = E::to_acc(__ldg(row + blank));
         const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
@@ -99,7 +94,7 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_r
                 E::unpack(v[j], e);
 #pragma unroll
                 for (int c = 0; c < VE; ++c) e[c] = exp_shifted(e[c], lse_a) * tot;
-                st_stream(ov + j * LPR + gl, E::pack(e));
+                ov[j * LPR + gl] = E::pack(e);
             }
         }
         // the two sparse corrections, by the lane that stored the enclosing vector (same-thread program order)
@@ -110,7 +105,7 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_r
         }
         if (label >= 0 && label != blank && (label / VE) % LPR == gl)
             orow[label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
-        if (RUNS) rw.advance(w.off, B, lx, ly);
+        rw.advance(w.off, B, lx, ly);
     }
 }
 
@@ -218,7 +213,7 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     const bool aligned = (p.V % VE == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                          (reinterpret_cast<uintptr_t>(gx) % 16 == 0);
     if (!(p.flags & CWRNNT_FUSED_LOG_SOFTMAX)) {
-        static const int grid = resident_grid(grad_rows_sparse_kernel<T>, kStreamThreads);
+        const unsigned grid = tiled_grid(p.n_rows, 8 * 4);  // 8 warps, 4 rows each
         grad_rows_sparse_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
                                                                    p.blank, p.flags, mean_inv, w, gc, gc_stride,
                                                                    aligned ? 1 : 0);
@@ -227,30 +222,28 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     RowShape shape{};
     if (aligned && pick_row_shape(p.V / VE, &shape)) {
         const bool full = (p.V / VE) == shape.lpr * shape.nv;
-        // Row assignment, measured on B200: rows of 2 KB and more stream best when a CTA takes 8 consecutive rows per
-        // iteration and strides by the grid (443 us vs 455 us at V=1024 float32: fewer DRAM pages open at once for
-        // the mixed read/write stream); short rows are bound by per-row instructions and prefer contiguous runs
-        // (435 us vs 575 us at V=128 float16).
-        const bool runs = int64_t(p.V) * int64_t(sizeof(T)) < 2048;
-#define LAUNCH(LPR, NV, FULL, RUNS)                                                                               \
-    {                                                                                                             \
-        static const int resident = resident_grid(grad_rows_kernel<T, LPR, NV, FULL, RUNS>, kStreamThreads);      \
-        const int grid = RUNS ? resident : 2 * resident; /* strided tiles: two waves even out the tail */         \
-        grad_rows_kernel<T, LPR, NV, FULL, RUNS><<<grid, kStreamThreads, 0, s>>>(                                 \
-            x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride);      \
+        // rows per lane group, measured 1..32 on B200: a tile of 8 rows x 4 KB (run 1) or 16 rows x 2 KB (run 2)
+        // per CTA streams best for the mixed read/write pattern; short rows are bound by per-row instructions and
+        // want longer runs, and so do 8 KB rows, whose 16 vector registers per lane leave few warps per SM
+        const int64_t row_bytes = int64_t(p.V) * int64_t(sizeof(T));
+        const int run_len = row_bytes >= 8192 ? 8 : (row_bytes >= 4096 ? 1 : (row_bytes >= 2048 ? 2 : 8));
+#define LAUNCH(LPR, NV, FULL)                                                                                    \
+    {                                                                                                            \
+        const unsigned grid = tiled_grid(p.n_rows, int64_t(kStreamThreads / LPR) * run_len);                     \
+        grad_rows_kernel<T, LPR, NV, FULL><<<grid, kStreamThreads, 0, s>>>(                                      \
+            x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride,      \
+            run_len);                                                                                            \
     }
-#define CALL(LPR, NV)                                \
-    {                                                \
-        if (full && runs) LAUNCH(LPR, NV, true, true)        \
-        else if (full) LAUNCH(LPR, NV, true, false)          \
-        else if (runs) LAUNCH(LPR, NV, false, true)          \
-        else LAUNCH(LPR, NV, false, false)                   \
+#define CALL(LPR, NV)                    \
+    {                                    \
+        if (full) LAUNCH(LPR, NV, true)  \
+        else LAUNCH(LPR, NV, false)      \
     }
         CWRNNT_DISPATCH_SHAPE(shape, CALL);
 #undef CALL
 #undef LAUNCH
     } else {
-        static const int grid = resident_grid(grad_rows_generic_kernel<T>, kStreamThreads);
+        const unsigned grid = tiled_grid(p.n_rows, 8 * 4);
         grad_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
                                                                     p.blank, p.flags, mean_inv, w, gc, gc_stride);
     }

@@ -6,19 +6,21 @@
 // cell (d-u, u) at step d, so no CTA ever waits on another:
 //   alpha(t,u) = LSE(alpha(t-1,u) + blank(t-1,u), alpha(t,u-1) + label(t,u-1)),  alpha(0,0) = 0     (:59-125)
 //   beta(t,u)  = LSE(beta(t+1,u) + blank(t,u),    beta(t,u+1) + label(t,u)),     beta(T-1,U) = blank(T-1,U)  (:165-231)
-// The own-column operand stays in a register, the neighbour column arrives by warp shuffle (shared memory only at warp
-// seams, one named barrier per diagonal). The log-probs K1 wrote diagonal-major are one contiguous stream per
-// (sequence, direction): each thread stages its own operands, several diagonals ahead of the dependent chain, with
-// 8-byte cp.async copies into a shared-memory ring (fully coalesced across the warp, and no register scoreboard is
-// held while they fly). alpha and beta are written diagonal-major too, so a warp's store is one contiguous 256-byte
-// segment. alpha and beta CTAs of all sequences run concurrently in one launch, longest critical path first.
+// Two kernels share the recursion. Lattices of up to 512 columns take the split-role kernel (further down): a compute
+// warp and a helper warp per 32 columns. Wider ones take the single-role kernel: the own-column operand stays in a
+// register, the neighbour column arrives by warp shuffle (shared memory only at warp seams), one named barrier per
+// diagonal, 1, 4 or 8 columns per thread. In both, the log-probs K1 wrote diagonal-major form one contiguous stream
+// per (sequence, direction); each thread stages its own operands, several diagonals ahead of the dependent chain,
+// with 8-byte cp.async copies into a shared-memory ring (fully coalesced across the warp, and no register scoreboard
+// is held while they fly). alpha and beta are written diagonal-major too, so a warp's store is one contiguous
+// 256-byte segment. alpha and beta CTAs of all sequences run concurrently in one launch, longest critical path first.
 // (A producer/consumer variant - one elected thread feeding the ring with cp.async.bulk + mbarrier - was built and
 // measured: 125 us against 79 us on the 81-column workload, because its per-step chunk bookkeeping costs more
 // instructions on the dependent chain than the per-thread copies it replaces; it was dropped.)
 //
 // Arithmetic: the running sums are kept in double (|alpha| reaches 10^3..10^4, where a float ulp is ~1e-4 and would
-// show up directly in exp(alpha+beta-ll)); the bounded correction log1p(exp(-|a-b|)) is evaluated in float as in the
-// reference (:10,:22-29), or in double for double input.
+// show up directly in exp(alpha+beta-ll)); the bounded correction log1p(exp(-|a-b|)) is evaluated in float (the
+// reference evaluates its whole log-sum-exp in float, :10,:22-29), or in double for double input.
 //
 // Bound: latency of the dependent chain, T+U steps per sequence; reported as microseconds per diagonal.
 // The last CTA to finish turns the per-sequence log-likelihoods into costs, the status bits and the reduced loss.
