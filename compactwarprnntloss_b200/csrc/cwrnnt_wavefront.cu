@@ -401,34 +401,38 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
     const int nd = T + U;
     double *st_b = stage + u;                    // slot k at st_b[k * n_cols]
     double *st_l = stage + R * n_cols + u;
-    double *v0 = vbuf, *v1 = vbuf + n_cols;      // results of even / odd steps
+    // results of even / odd steps; element n_cols of each row is a permanent -inf (the neighbour of an edge column)
+    double *v0 = vbuf, *v1 = vbuf + n_cols + 1;
 
     if (helper) {
-        DiagCursor pf;
-        pf.T = T;
-        pf.U = U;
-        if (!BETA) {
-            pf.e = -1;
-            pf.base = 0;
-        } else {
-            pf.e = nd - 1;
-            pf.base = T * m - 1 - U;
-        }
+        // Diagonal e starts at stream element base(e) + lo(e) and column u sits at base(e) + u; moving to the next
+        // diagonal adds step(e) = min(e+1, c2, U+T-1-e), c2 = (U <= T-1) ? U+1 : T-1 (growing, plateau, shrinking
+        // part of the lattice). e = diagonal whose operands are staged next, tb = e - u.
+        const int c2 = (U <= T - 1) ? U + 1 : T - 1;
+        int e = BETA ? nd - 1 : -1;
+        int base = BETA ? T * m - 1 - U : 0;
+        int tb = u <= U ? e - u : INT_MIN / 2;  // parked far outside every range for columns beyond U
         int sbase[R];
         auto issue = [&](int k) {
-            sbase[k] = pf.base;
-            const int tb = pf.e - u;
+            sbase[k] = base;
             double *sb = st_b + k * n_cols, *sl = st_l + k * n_cols;
             if (!BETA) {
-                if (u <= U && tb >= 0 && tb <= T - 2) cp_async8(sb, lpb + pf.base + u); else *sb = 0.0;
-                if (u <= U && u >= 1 && tb >= -1 && tb <= T - 2) cp_async8(sl, lpl + pf.base + u - 1); else *sl = 0.0;
+                // step e+1 at column u needs blank(e-u, u) and label(e-u+1, u-1)
+                if (unsigned(tb) < unsigned(T - 1)) cp_async8(sb, lpb + base + u); else *sb = 0.0;
+                if (u >= 1 && unsigned(tb + 1) < unsigned(T)) cp_async8(sl, lpl + base + u - 1); else *sl = 0.0;
+                if (e >= 0) base += min(min(e + 1, c2), U + T - 1 - e);
+                ++e;
+                ++tb;
             } else {
-                const bool cell = u <= U && tb >= 0 && tb <= T - 1;
-                if (cell) cp_async8(sb, lpb + pf.base + u); else *sb = 0.0;
-                if (cell && u < U) cp_async8(sl, lpl + pf.base + u); else *sl = 0.0;
+                // step with d = e at column u needs blank(e-u, u) and label(e-u, u)
+                const bool cell = unsigned(tb) < unsigned(T);
+                if (cell) cp_async8(sb, lpb + base + u); else *sb = 0.0;
+                if (cell && u < U) cp_async8(sl, lpl + base + u); else *sl = 0.0;
+                --e;
+                --tb;
+                if (e >= 0) base -= min(min(e + 1, c2), U + T - 1 - e);
             }
             cp_async_commit();
-            if (!BETA) pf.up(); else pf.down();
         };
 #pragma unroll
         for (int k = 0; k < R; ++k) issue(k);
@@ -448,7 +452,8 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
                 const int this_base = sbase[k];
                 const int out_base = BETA ? last_base : this_base;
                 last_base = this_base;
-                if (s >= 1 && unsigned(tprev) < unsigned(T)) out[out_base + u] = ((s - 1) & 1) ? v1[u] : v0[u];
+                // R is even and s0 a multiple of R: the parity of s is the parity of k
+                if (s >= 1 && unsigned(tprev) < unsigned(T)) out[out_base + u] = (k & 1) ? v0[u] : v1[u];
                 tprev += BETA ? -1 : 1;
                 if (s == nd) break;  // last round only drains the final result
                 issue(k);
@@ -460,23 +465,27 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
         return;
     }
 
-    // ---- compute warp
+    // ---- compute warp. Cells outside the lattice count as -inf: both result rows start at -inf (the "previous
+    // step" of step 0 and every column's virtual predecessor row), and edge columns read the permanent -inf element.
+    v0[u] = -INFINITY;
+    v1[u] = -INFINITY;
+    if (u == 0) {
+        v0[n_cols] = -INFINITY;
+        v1[n_cols] = -INFINITY;
+    }
     double prev = (u == (BETA ? U : 0)) ? 0.0 : -INFINITY;
-    const bool no_neighbour = BETA ? (u >= U) : (u == 0);
-    const int nb_col = BETA ? min(u + 1, n_cols - 1) : max(u - 1, 0);
+    const int nb_col = BETA ? (u >= U ? n_cols : u + 1) : (u == 0 ? n_cols : u - 1);
     asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");  // start barrier: operands of steps 0 and 1 are staged
     double cur_b = st_b[0], cur_l = st_l[0];
     for (int s0 = 0; s0 < nd; s0 += R) {
 #pragma unroll
         for (int k = 0; k < R; ++k) {
-            const int s = s0 + k;
-            if (s >= nd) break;
+            if (s0 + k >= nd) break;
             const double nxt_b = st_b[((k + 1) % R) * n_cols];
             const double nxt_l = st_l[((k + 1) % R) * n_cols];
-            double nb = (s & 1) ? v0[nb_col] : v1[nb_col];  // the neighbour's result of step s-1
-            if (no_neighbour || s == 0) nb = -INFINITY;      // step 0 starts from the virtual row
+            const double nb = (k & 1) ? v0[nb_col] : v1[nb_col];  // the neighbour's result of the previous step
             const double v = lse2<F64>(prev + cur_b, nb + cur_l, lse_tab);
-            if (s & 1) v1[u] = v; else v0[u] = v;
+            if (k & 1) v1[u] = v; else v0[u] = v;
             prev = v;
             cur_b = nxt_b;
             cur_l = nxt_l;
@@ -569,7 +578,7 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
         constexpr int R = 8;
         const int half = (cols + 31) & ~31;
         const int threads = 2 * half;
-        const size_t smem = size_t(2 * R + 2) * half * sizeof(double);
+        const size_t smem = (size_t(2 * R + 2) * half + 2) * sizeof(double);
         if ((e = opt_in_smem(wavefront_split_kernel<R, F64>, smem, threads)) != cudaSuccess) return e;
         wavefront_split_kernel<R, F64><<<grid, threads, smem, s>>>(g);
         return cudaGetLastError();
