@@ -75,6 +75,7 @@ static int forward_impl(const cwrnnt_problem *p, const void *x, const int32_t *l
 {
     int st = check_problem(p);
     if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;  // an empty batch: nothing to read, nothing to write
     if (!lx || !ly || !costs || (p->n_rows > 0 && !x) || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
     Workspace w{};
     st = check_workspace(p, workspace, workspace_bytes, &w);
@@ -110,6 +111,7 @@ int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, c
     int st = check_problem(p);
     if (st) return st;
     if (p->flags & CWRNNT_COSTS_ONLY) return CWRNNT_ERR_ARGUMENT;  // that forward kept no alpha
+    if (p->B == 0) return CWRNNT_OK;
     if (!lx || !ly || (p->n_rows > 0 && (!x || !grad_x)) || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
     if (grad_costs_stride != 0 && grad_costs_stride != 1) return CWRNNT_ERR_ARGUMENT;
     Workspace w{};

@@ -100,6 +100,27 @@ def test_wide_and_long_lattices(oracle, T, U):
     _check_fused(oracle, case)
 
 
+def test_long_form_sequence_against_oracle(oracle):
+    """One sequence of the long-form workload's size (T=1200, U=300, V=512: 1900 diagonals, 301 columns = 10 compute
+    and 10 helper warps in the wavefront kernel)."""
+    case = ragged_case(4, 1, (1200, 1200), (300, 300), V=512, sigma=1.0)
+    _check_fused(oracle, case, reduce="mean")
+
+
+def test_empty_batch_and_tiny_batches_launch_nothing_harmful():
+    from compactwarprnntloss_b200 import capi
+    dev = torch.device("cuda:0")
+    x = torch.zeros(0, 8, device=dev)
+    lx = torch.zeros(0, dtype=torch.int32, device=dev)
+    y = torch.zeros(0, 0, dtype=torch.int32, device=dev)
+    p = capi.make_problem(x, lx, y, 0, capi.FUSED_LOG_SOFTMAX)
+    ws = capi.alloc_workspace(p, dev)
+    costs = torch.zeros(1, device=dev)
+    capi.forward(p, x, lx, lx, y, ws, costs)           # B = 0: accepted, nothing to do
+    capi.backward(p, x, lx, lx, y, ws, None, 0, x)
+    torch.cuda.synchronize()
+
+
 def test_many_sequences_order_and_cursor(oracle):
     case = ragged_case(31, 300, (1, 12), (0, 6), V=8)
     _check_fused(oracle, case, reduce="mean")

@@ -136,3 +136,25 @@ def test_offsets_and_empty_labels(oracle):
     lp = oracle.log_softmax(x)
     assert abs(costs[0] + lp[0:3, 2].sum()) < 1e-12
     assert abs(costs[1] + lp[3, 2]) < 1e-12
+
+
+def test_property_random_tiny_lattices_match_brute_force(oracle):
+    """Property test over ragged shapes (hypothesis): double flavour == path enumeration, float flavour close."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=40, deadline=None)
+    @given(T=st.integers(1, 5), U=st.integers(0, 4), V=st.integers(2, 6), seed=st.integers(0, 10 ** 6),
+           blank=st.integers(0, 1))
+    def run(T, U, V, seed, blank):
+        c = ragged_case(seed, 1, (T, T), (U, U), V=V, blank=blank, allow_blank_label=True)
+        lp = oracle.log_softmax(c["x"])
+        g = oracle.gather(lp, c["lx"], c["ly"], c["y"], blank)
+        fw = oracle.forward(g, c["lx"], c["ly"])
+        want = oracle.brute_force_cost(g[:, 0].reshape(T, U + 1).tolist(), g[:, 1].reshape(T, U + 1).tolist())
+        assert abs(fw["costs"][0] - want) < 1e-9
+        f32 = oracle.forward_ref32(g.astype(np.float32), c["lx"], c["ly"])
+        assert abs(f32["costs"][0] - want) < 1e-4 * max(1.0, abs(want))
+        costs, dense = oracle.fused(c["x"], c["lx"], c["ly"], c["y"], blank)
+        assert abs(costs[0] - want) < 1e-9 and np.abs(dense.sum(-1)).max() < 1e-12
+
+    run()
