@@ -24,7 +24,10 @@ OUT = os.path.join(HERE, "_ref")
 NAME = "cwarp_rnnt_ref_C"
 
 
-def build(ref_root: str = "/root/reference", verbose: bool = False) -> str:
+DEFAULT_REFERENCE_ROOT = os.environ.get("CWRNNT_REFERENCE_ROOT", "/root/reference")
+
+
+def build(ref_root: str = DEFAULT_REFERENCE_ROOT, verbose: bool = False) -> str:
     srcs = [os.path.join(ref_root, f) for f in
             ("cwarp_cuda.cpp", "cwarp_cuda_gather_kernel.cu", "cwarp_cuda_rnnt_kernel.cu")]
     for s in srcs:
