@@ -26,6 +26,7 @@ EXPORTS = [
     "cwrnnt_backward", "cwrnnt_pair_grads", "cwrnnt_export_alpha_beta", "cwrnnt_scatter_scratch_bytes",
     "cwrnnt_scatter_backward", "cwrnnt_read_status", "cwrnnt_host_ctx_create", "cwrnnt_host_ctx_destroy",
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
+    "cwrnnt_pack_padded", "cwrnnt_unpack_padded",
 ]
 
 
@@ -65,6 +66,8 @@ def lib():
         L.cwrnnt_scatter_scratch_bytes.restype = i64
         L.cwrnnt_scatter_scratch_bytes.argtypes = [i32]
         L.cwrnnt_scatter_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i64, vp, vp]
+        L.cwrnnt_pack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
+        L.cwrnnt_unpack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_costs_static.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_read_status.argtypes = [vp, ctypes.POINTER(i32 * 4), vp]
         L.cwrnnt_host_ctx_create.argtypes = [ctypes.POINTER(vp)]
@@ -164,6 +167,33 @@ def scatter_backward(p: Problem, grads, grad_costs, lx, ly, y, dense) -> None:
         check(lib().cwrnnt_scatter_backward(ctypes.byref(p), _ptr(grads), _ptr(grad_costs), _ptr(lx), _ptr(ly),
                                             _ptr(y), _ptr(scratch), n, _ptr(dense), _stream(grads.device)),
               "cwrnnt_scatter_backward")
+
+
+def pack_padded(padded: torch.Tensor, lx, ly, n_rows: int) -> torch.Tensor:
+    """[B, T, U+1, V] -> compact [n_rows, V] keeping padded[n, :lx[n], :ly[n]+1] of every sequence."""
+    B, T, Up, V = padded.shape
+    out = torch.empty(n_rows, V, dtype=padded.dtype, device=padded.device)
+    p = Problem(n_rows=n_rows, V=V, B=B, y_stride=Up - 1, max_u=Up - 1, blank=0, dtype=dtype_code(padded.dtype))
+    n = lib().cwrnnt_scatter_scratch_bytes(B)
+    scratch = torch.empty(n, dtype=torch.uint8, device=padded.device)
+    with torch.cuda.device(padded.device):
+        check(lib().cwrnnt_pack_padded(ctypes.byref(p), _ptr(padded), T, Up, _ptr(lx), _ptr(ly), _ptr(scratch), n,
+                                       _ptr(out), _stream(padded.device)), "cwrnnt_pack_padded")
+    return out
+
+
+def unpack_padded(compact: torch.Tensor, lx, ly, B: int, T: int, Up: int) -> torch.Tensor:
+    """Transpose of pack_padded: compact rows back into a zero-padded [B, T, U+1, V] tensor."""
+    V = compact.size(1)
+    out = torch.empty(B, T, Up, V, dtype=compact.dtype, device=compact.device)
+    p = Problem(n_rows=compact.size(0), V=V, B=B, y_stride=Up - 1, max_u=Up - 1, blank=0,
+                dtype=dtype_code(compact.dtype))
+    n = lib().cwrnnt_scatter_scratch_bytes(B)
+    scratch = torch.empty(n, dtype=torch.uint8, device=compact.device)
+    with torch.cuda.device(compact.device):
+        check(lib().cwrnnt_unpack_padded(ctypes.byref(p), _ptr(compact), T, Up, _ptr(lx), _ptr(ly), _ptr(scratch), n,
+                                         _ptr(out), _stream(compact.device)), "cwrnnt_unpack_padded")
+    return out
 
 
 def costs_static(p: Problem, x, lx, ly, y, costs, loss=None) -> None:

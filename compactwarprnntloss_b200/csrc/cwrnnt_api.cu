@@ -174,6 +174,37 @@ int cwrnnt_scatter_backward(const cwrnnt_problem *p, const void *grads, const vo
     return e == cudaSuccess ? CWRNNT_OK : fail_launch("scatter_backward", e);
 }
 
+static int pack_impl(const cwrnnt_problem *p, bool to_compact, const void *src, void *dst, int32_t t_max,
+                     int32_t u_max1, const int32_t *lx, const int32_t *ly, void *scratch, int64_t scratch_bytes,
+                     cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    if (!lx || !ly || t_max < 0 || u_max1 < 1 || u_max1 < p->max_u + 1) return CWRNNT_ERR_ARGUMENT;
+    const int64_t padded_rows = int64_t(p->B) * t_max * u_max1;
+    if ((p->n_rows > 0 && !(to_compact ? dst : src)) || (padded_rows > 0 && !(to_compact ? src : dst)))
+        return CWRNNT_ERR_ARGUMENT;
+    if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 8 != 0 || scratch_bytes < cwrnnt_scatter_scratch_bytes(p->B))
+        return CWRNNT_ERR_WORKSPACE;
+    cudaError_t e = launch_pack(*p, to_compact, src, dst, t_max, u_max1, lx, ly, static_cast<int64_t *>(scratch),
+                                reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch(to_compact ? "pack_padded" : "unpack_padded", e);
+}
+
+int cwrnnt_pack_padded(const cwrnnt_problem *p, const void *padded, int32_t t_max, int32_t u_max1, const int32_t *lx,
+                       const int32_t *ly, void *scratch, int64_t scratch_bytes, void *compact, cwrnnt_stream_t stream)
+{
+    return pack_impl(p, true, padded, compact, t_max, u_max1, lx, ly, scratch, scratch_bytes, stream);
+}
+
+int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact, int32_t t_max, int32_t u_max1,
+                         const int32_t *lx, const int32_t *ly, void *scratch, int64_t scratch_bytes, void *padded,
+                         cwrnnt_stream_t stream)
+{
+    return pack_impl(p, false, compact, padded, t_max, u_max1, lx, ly, scratch, scratch_bytes, stream);
+}
+
 int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream)
 {
     if (!workspace || !out) return CWRNNT_ERR_ARGUMENT;

@@ -41,4 +41,9 @@ cudaError_t launch_export_ab(const cwrnnt_problem &p, const int32_t *lx, const i
 cudaError_t launch_scatter(const cwrnnt_problem &p, const void *grads, const void *grad_costs, const int32_t *lx,
                            const int32_t *ly, const int32_t *y, int64_t *off_scratch, void *dense, cudaStream_t s);
 
+// Padded [B, t_max, u_max1, V] <-> compact [n_rows, V] (to_compact: src padded, dst compact; else the transpose,
+// zero-filling the padding).
+cudaError_t launch_pack(const cwrnnt_problem &p, bool to_compact, const void *src, void *dst, int32_t t_max,
+                        int32_t u_max1, const int32_t *lx, const int32_t *ly, int64_t *off_scratch, cudaStream_t s);
+
 }  // namespace cwrnnt

@@ -141,6 +141,54 @@ std::vector<int64_t> rnnt_status(const torch::Tensor &workspace)
     return {st[0], st[1], st[2], st[3]};
 }
 
+// Padded [N, T, U+1, V] -> compact [n_rows, V] (n_rows = sum T_n*(U_n+1), computed by the caller) and back.
+torch::Tensor pack_padded(const torch::Tensor &padded, const torch::Tensor &lx, const torch::Tensor &ly,
+                          int64_t n_rows)
+{
+    CHECK_CUDA(padded);
+    CHECK_CONTIGUOUS(padded);
+    CHECK_INPUT(lx, torch::ScalarType::Int);
+    CHECK_INPUT(ly, torch::ScalarType::Int);
+    TORCH_CHECK(padded.dim() == 4 && padded.size(0) == lx.size(0), "padded must be [N, T, U+1, V]");
+    const c10::cuda::CUDAGuard guard(padded.device());
+    cwrnnt_problem p{};
+    p.n_rows = n_rows;
+    p.V = static_cast<int32_t>(padded.size(3));
+    p.B = static_cast<int32_t>(padded.size(0));
+    p.y_stride = p.max_u = static_cast<int32_t>(padded.size(2) - 1);
+    p.dtype = dtype_code(padded);
+    auto scratch = torch::empty({cwrnnt_scatter_scratch_bytes(p.B)}, padded.options().dtype(torch::kUInt8));
+    auto out = torch::empty({n_rows, padded.size(3)}, padded.options());
+    check_status(cwrnnt_pack_padded(&p, padded.data_ptr(), static_cast<int32_t>(padded.size(1)),
+                                    static_cast<int32_t>(padded.size(2)), i32(lx), i32(ly), scratch.data_ptr(),
+                                    scratch.numel(), out.data_ptr(), current_stream()),
+                 "cwrnnt_pack_padded");
+    return out;
+}
+
+torch::Tensor unpack_padded(const torch::Tensor &compact, const torch::Tensor &lx, const torch::Tensor &ly,
+                            int64_t T, int64_t Up)
+{
+    CHECK_CUDA(compact);
+    CHECK_INPUT(lx, torch::ScalarType::Int);
+    CHECK_INPUT(ly, torch::ScalarType::Int);
+    TORCH_CHECK(compact.dim() == 2, "compact must be [n_rows, V]");
+    const c10::cuda::CUDAGuard guard(compact.device());
+    auto c = compact.contiguous();
+    cwrnnt_problem p{};
+    p.n_rows = c.size(0);
+    p.V = static_cast<int32_t>(c.size(1));
+    p.B = static_cast<int32_t>(lx.size(0));
+    p.y_stride = p.max_u = static_cast<int32_t>(Up - 1);
+    p.dtype = dtype_code(c);
+    auto scratch = torch::empty({cwrnnt_scatter_scratch_bytes(p.B)}, c.options().dtype(torch::kUInt8));
+    auto out = torch::empty({lx.size(0), T, Up, c.size(1)}, c.options());
+    check_status(cwrnnt_unpack_padded(&p, c.data_ptr(), static_cast<int32_t>(T), static_cast<int32_t>(Up), i32(lx),
+                                      i32(ly), scratch.data_ptr(), scratch.numel(), out.data_ptr(), current_stream()),
+                 "cwrnnt_unpack_padded");
+    return out;
+}
+
 // ------------------------------------------------------------------- the reference module's functions, same shapes
 
 // cwarp_cuda.cpp:84-108. xs are log-probabilities. Returns (costs [N], grads [STU,2], alphas, betas [N,Tmax,Umax+1]).
@@ -235,6 +283,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("_rnnt_forward", &rnnt_forward, "Fused forward: (costs, loss, workspace).");
     m.def("_rnnt_backward", &rnnt_backward, "Fused backward: gradient w.r.t. xs.");
     m.def("_rnnt_status", &rnnt_status, "Status words of a workspace (synchronises).");
+    m.def("_pack_padded", &pack_padded, "Padded [N,T,U+1,V] -> compact [n_rows,V].");
+    m.def("_unpack_padded", &unpack_padded, "Compact [n_rows,V] -> zero-padded [N,T,U+1,V].");
     m.attr("FUSED_LOG_SOFTMAX") = static_cast<int>(CWRNNT_FUSED_LOG_SOFTMAX);
     m.attr("COSTS_ONLY") = static_cast<int>(CWRNNT_COSTS_ONLY);
     m.attr("REDUCE_MEAN") = static_cast<int>(CWRNNT_REDUCE_MEAN);

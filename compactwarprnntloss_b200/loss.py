@@ -60,14 +60,25 @@ class _TransLoss(torch.autograd.Function):
         return grad_x, None, None, None, None, None, None, None
 
 
+class _PackPadded(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx: Any, x, lx, ly, n_rows):
+        ctx.save_for_backward(lx, ly)
+        ctx.shape = x.shape
+        return core._pack_padded(x.contiguous(), lx, ly, n_rows)
+
+    @staticmethod
+    def backward(ctx: Any, grad):
+        lx, ly = ctx.saved_tensors
+        return core._unpack_padded(grad, lx, ly, ctx.shape[1], ctx.shape[2]), None, None, None
+
+
 def compact_from_padded(x: torch.Tensor, lx: torch.Tensor, ly: torch.Tensor) -> torch.Tensor:
     """[N, T, U+1, V] padded joint output -> compact [sum_i T_i*(U_i+1), V], keeping x[i, :T_i, :U_i+1] of every
-    sequence in (t, u) row-major order (the layout of the reference's test/test.py:34-48). Differentiable."""
-    N, T, Up, V = x.shape
-    t_ok = torch.arange(T, device=x.device)[None, :] < lx[:, None].to(x.device)
-    u_ok = torch.arange(Up, device=x.device)[None, :] <= ly[:, None].to(x.device)
-    mask = t_ok[:, :, None] & u_ok[:, None, :]
-    return x[mask]
+    sequence in (t, u) row-major order (the layout of the reference's test/test.py:34-48). Differentiable: the
+    gradient is scattered back into a zero-padded tensor. Reads the lengths on the host once for the row count."""
+    n_rows = int((lx.long() * (ly.long() + 1)).sum())
+    return _PackPadded.apply(x, lx, ly, n_rows)
 
 
 def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torch.Tensor, blank: int = 0,

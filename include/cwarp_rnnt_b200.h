@@ -166,6 +166,21 @@ CWRNNT_API int cwrnnt_scatter_backward(const cwrnnt_problem *p, const void *grad
                             cwrnnt_stream_t stream);
 
 /*
+ * Padded joint output [B, t_max, u_max1, V] -> compact [n_rows, V] and its transpose for the gradient (which also
+ * zero-fills the padding). Replaces the reference's 4-D convenience path, gather.cat on the flattened [T*(U+1)] axis
+ * (cwarp_rnnt/__init__.py:52-59) - with the per-sequence slicing its own test defines, x[n, :T_n, :U_n+1, :]
+ * (test/test.py:45-46); the reference's version is only right when every U_n equals Umax. p supplies n_rows, V, B,
+ * dtype and max_u (<= u_max1 - 1); `scratch` needs cwrnnt_scatter_scratch_bytes(B) bytes. When sum T_n*(U_n+1)
+ * differs from n_rows the pack leaves `compact` untouched and the unpack writes zeros only.
+ */
+CWRNNT_API int cwrnnt_pack_padded(const cwrnnt_problem *p, const void *padded, int32_t t_max, int32_t u_max1,
+                                  const int32_t *lx, const int32_t *ly, void *scratch, int64_t scratch_bytes,
+                                  void *compact, cwrnnt_stream_t stream);
+CWRNNT_API int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact, int32_t t_max, int32_t u_max1,
+                                    const int32_t *lx, const int32_t *ly, void *scratch, int64_t scratch_bytes,
+                                    void *padded, cwrnnt_stream_t stream);
+
+/*
  * Copies the 4 int32 status words of a workspace to HOST memory `out` and waits for the stream (the one call here
  * that synchronises). out[0] = CWRNNT_ST_* bits, out[1] = first offending sequence (-1 if none), out[2] = computed
  * sum of T_n*(U_n+1) (low 31 bits), out[3] = reserved. Replaces the reference's device printf warning

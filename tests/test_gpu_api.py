@@ -221,3 +221,22 @@ def test_forward_backward_capture_in_a_cuda_graph(oracle):
         np.testing.assert_allclose(costs.cpu().numpy(), c64, rtol=1e-5)
         assert abs(float(loss) - c64.mean()) <= 1e-5 * c64.mean()
         assert np.abs(gx.cpu().numpy() - d64).max() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype,V", [(torch.float32, 7), (torch.float32, 64), (torch.bfloat16, 40), (torch.float64, 6)])
+def test_pack_and_unpack_padded_through_the_c_abi(dtype, V):
+    """Padded [N,T,U+1,V] -> compact rows (x[n, :T_n, :U_n+1] per sequence, reference test/test.py:45-46) and the
+    transpose used for the gradient, which zero-fills the padding. Bit-exact copies."""
+    from compactwarprnntloss_b200 import capi
+    rng = np.random.default_rng(V)
+    N, T, Up = 5, 11, 6
+    lx = rng.integers(1, T + 1, size=N).astype(np.int32)
+    ly = rng.integers(0, Up, size=N).astype(np.int32)
+    xp = torch.tensor(rng.standard_normal((N, T, Up, V))).to(dtype).to(DEV)
+    want = torch.cat([xp[n, :lx[n], :ly[n] + 1].reshape(-1, V) for n in range(N)])
+    got = capi.pack_padded(xp, torch.tensor(lx, device=DEV), torch.tensor(ly, device=DEV), want.shape[0])
+    assert torch.equal(got, want)
+    back = capi.unpack_padded(got, torch.tensor(lx, device=DEV), torch.tensor(ly, device=DEV), N, T, Up)
+    for n in range(N):
+        assert torch.equal(back[n, :lx[n], :ly[n] + 1], xp[n, :lx[n], :ly[n] + 1])
+        assert back[n, lx[n]:].abs().sum() == 0 and back[n, :, ly[n] + 1:].abs().sum() == 0
