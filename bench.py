@@ -47,7 +47,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"],
+                    help="ours: this engine; reference: the path's CPU implementation on the host cores; "
+                         "reference_cuda: the reference project's own CUDA kernels rebuilt for sm_100a (oracle/_ref)")
     ap.add_argument("--cfg", type=int, default=2, help="workload (1-5); the headline metric is quoted on 2")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -214,10 +216,60 @@ def run_reference(args):
     }))
 
 
+def run_reference_cuda(args):
+    """The reference's own pipeline on one GPU: torch.log_softmax -> its _cwarp_rnnt_forward -> its
+    _cwarp_rnnt_backward -> log_softmax backward, float32, device-resident inputs, CUDA events. Extra comparator
+    (not the CPU reference arm); needs oracle/_ref/cwarp_rnnt_ref_C.so, built by oracle/build_ref.py."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from oracle.build_ref import load_ref
+    ref = load_ref()
+    if ref is None or not torch.cuda.is_available():
+        print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref/cwarp_rnnt_ref_C.so not built or no GPU"}))
+        return
+    cfg = args.cfg
+    wl = synth.WORKLOADS[cfg]
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    lx, ly, y = synth.lengths_and_labels(cfg)
+    x = synth.compact_logits(cfg, lx, ly).float().to(dev).requires_grad_(True)
+    lxd, lyd, yd = lx.to(dev), ly.to(dev), y.to(dev).contiguous()
+    gc = torch.full((len(lx),), 1.0 / len(lx), device=dev)
+    nodes = x.shape[0]
+
+    def step():
+        x.grad = None
+        lp = torch.log_softmax(x, -1)
+        costs, grads, _, _ = ref._cwarp_rnnt_forward(lp, lxd, yd, lyd, 0)
+        dense = ref._cwarp_rnnt_backward(grads, gc, yd, lxd, lyd, 0, wl.V)
+        lp.backward(dense)
+        return costs
+
+    for _ in range(max(args.warmup, 3)):
+        costs = step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        costs = step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({
+        "impl": "reference_cuda", "metric": METRIC, "value": nodes / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "f32", "data": "synthetic", "loss": float(costs.mean()),
+        "config": {"workload": wl.name, "lattice_nodes": nodes,
+                   "pipeline": "torch.log_softmax + reference _cwarp_rnnt_forward/_backward (sm_100a rebuild of its "
+                               "unmodified sources) + log_softmax backward"}}))
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "reference_cuda":
+        return run_reference_cuda(args)
 
     from compactwarprnntloss_b200 import capi, sharding
     import torch.distributed as dist
