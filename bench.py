@@ -51,6 +51,8 @@ def parse():
                     help="ours: this engine; reference: the path's CPU implementation on the host cores; "
                          "reference_cuda: the reference project's own CUDA kernels rebuilt for sm_100a (oracle/_ref)")
     ap.add_argument("--cfg", type=int, default=2, help="workload (1-5); the headline metric is quoted on 2")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: B*N sequences over N GPUs (default); strong: the workload's B sequences sharded over N")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-seqs", type=int, default=32,
@@ -287,7 +289,7 @@ def main():
     wl = synth.WORKLOADS[cfg]
 
     # ---- workload: weak scaling, B = wl.B * world sequences sharded by lattice size
-    B_global = wl.B * world
+    B_global = wl.B * world if args.scaling == "weak" else wl.B
     lx, ly, y = synth.lengths_and_labels(cfg, B=B_global)
     plan = sharding.plan_shards(lx.tolist(), ly.tolist(), world)
     sharding.validate_plan(plan, B_global)
@@ -409,7 +411,7 @@ def main():
     traffic = GRAD_KERNEL_DRAM_BYTES_PER_NODE.get(cfg)
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": {torch.float32: "f32", torch.float16: "f16", torch.bfloat16: "bf16"}[wl.dtype],
         "data": "synthetic",
         "config": {"workload": wl.name, "global_sequences": B_global, "lattice_nodes": nodes_global,

@@ -166,7 +166,11 @@ def test_extension_functions_against_golden_reference_outputs(oracle, path):
 
 def test_live_reference_cuda_kernels_when_built(oracle):
     """ours vs the reference's CUDA kernels (oracle/_ref, sm_100a build of its unmodified sources) on a Conformer-shape
-    lattice: loss within 1e-5 relative; gradients within the reference's own float32 error + 1e-5."""
+    lattice: costs within 1e-5 relative; gradients within the reference's own float32 error + 1e-5.
+
+    The reference's tile hand-over is racy on B200 (on large batches its own forward/backward guard fires and it returns
+    a wrong cost for the affected sequence), so sequences on which the reference disagrees with the double oracle by
+    more than 1e-4 relative are left out of the reference comparison; this engine is held to the oracle on all of them."""
     from oracle.build_ref import load_ref
     import cwarp_rnnt
     ref = load_ref()
@@ -180,15 +184,20 @@ def test_live_reference_cuda_kernels_when_built(oracle):
     dense_r = ref._cwarp_rnnt_backward(grads_r.clone(), torch.full((4,), 0.25, device=DEV), y, lx, ly, 0, 32)
     lp.backward(dense_r)
     b = x.clone().requires_grad_(True)
-    ours = cwarp_rnnt.transducer_loss(b, lx, y, ly, 0, "mean", fused_log_softmax=True)
-    ours.backward()
+    ours = cwarp_rnnt.transducer_loss(b, lx, y, ly, 0, "none", fused_log_softmax=True)
+    (ours * 0.25).sum().backward()
     costs64, dense64 = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, weights=np.full(4, 0.25))
-    ref_err = np.abs(a.grad.cpu().numpy() - dense64).max()
+    np.testing.assert_allclose(ours.detach().cpu().numpy(), costs64, rtol=1e-5)
     our_err = np.abs(b.grad.cpu().numpy() - dense64).max()
-    assert abs(float(ours) - float(costs_r.mean())) <= 1e-5 * abs(float(ours))
     assert our_err <= 1e-5
-    assert (a.grad - b.grad).abs().max().item() <= ref_err + 1e-5
-    print(f"|ours-f64| {our_err:.2e}  |ref-f64| {ref_err:.2e}  |ours-ref| {(a.grad - b.grad).abs().max().item():.2e}")
+    sane = np.abs(costs_r.cpu().numpy() - costs64) <= 1e-4 * np.abs(costs64)
+    off = np.concatenate([[0], np.cumsum(case["lx"].astype(np.int64) * (case["ly"] + 1))])
+    for n in np.nonzero(sane)[0]:
+        rows = slice(off[n], off[n + 1])
+        assert abs(float(ours[n]) - float(costs_r[n])) <= 1e-5 * abs(float(ours[n]))
+        ref_err = np.abs(a.grad[rows].cpu().numpy() - dense64[rows]).max()
+        assert (a.grad[rows] - b.grad[rows]).abs().max().item() <= ref_err + 1e-5
+    print(f"|ours-f64| {our_err:.2e}; reference consistent on {int(sane.sum())} of 4 sequences")
 
 
 def test_forward_backward_capture_in_a_cuda_graph(oracle):
