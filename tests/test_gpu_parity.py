@@ -93,9 +93,10 @@ def test_edge_shapes(oracle):
     _check_fused(oracle, c)
 
 
-@pytest.mark.parametrize("T,U", [(40, 31), (33, 32), (5, 200), (300, 70), (64, 1030), (20, 2100)])
+@pytest.mark.parametrize("T,U", [(40, 31), (33, 32), (5, 200), (300, 70), (12, 511), (30, 700), (64, 1030), (20, 2100)])
 def test_wide_and_long_lattices(oracle, T, U):
-    """Column counts that cross warp seams (32), CTA width (1024 -> 2 columns per thread) and 2048 (4 per thread)."""
+    """Column counts that cross warp seams (32), the split-role kernel's limit (512 columns), the one-column-per-thread
+    limit (1024 -> 4 columns per thread) and 2048 (8 per thread)."""
     case = ragged_case(T * 7 + U, 2, (T - 3, T), (U - 2, U), V=8, sigma=1.0)
     _check_fused(oracle, case)
 
@@ -124,6 +125,9 @@ def test_empty_batch_and_tiny_batches_launch_nothing_harmful():
 def test_many_sequences_order_and_cursor(oracle):
     case = ragged_case(31, 300, (1, 12), (0, 6), V=8)
     _check_fused(oracle, case, reduce="mean")
+    # more sequences than the longest-first sort handles (4096): identity order, 9000 wavefront CTAs
+    case = ragged_case(32, 4500, (1, 4), (0, 3), V=4)
+    _check_fused(oracle, case, reduce="sum")
 
 
 def test_costs_only_matches_full(oracle):
