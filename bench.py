@@ -53,6 +53,8 @@ def parse():
     ap.add_argument("--cfg", type=int, default=2, help="workload (1-5); the headline metric is quoted on 2")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
                     help="weak: B*N sequences over N GPUs (default); strong: the workload's B sequences sharded over N")
+    ap.add_argument("--groups", type=int, default=0,
+                    help="sequence groups of the pipelined step (0 = chosen by the library, 1 = no overlap)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-seqs", type=int, default=32,
@@ -313,17 +315,24 @@ def main():
     vec = torch.empty(B_global + 1, dtype=ct, device=dev)
     ids_dev = torch.tensor(ids, dtype=torch.int32, device=dev)
 
+    pipe = capi.Pipe(dev)
+    n_groups = capi.pipeline_groups(p, args.groups)
+
     def forward():
         if world == 1:
             capi.forward(p, x, lxd, lyd, yd, ws, costs, loss)
         else:
-            # the wavefront epilogue fills the global cost vector; one all-reduce is the whole exchange
             capi.forward_sharded(p, x, lxd, lyd, yd, ws, costs, loss, ids_dev, B_global, vec)
-            dist.all_reduce(vec, op=dist.ReduceOp.SUM)
 
     def step():
-        forward()
-        capi.backward(p, x, lxd, lyd, yd, ws, one, 0, gx)
+        # one pipelined call: K0, then per sequence group gather -> wavefront (side stream) -> gradient
+        if world == 1:
+            capi.loss_grad(p, x, lxd, lyd, yd, ws, costs, loss, one, 0, gx, pipe=pipe, groups=args.groups)
+        else:
+            # the wavefront epilogue fills the global cost vector; one all-reduce is the whole exchange
+            capi.loss_grad(p, x, lxd, lyd, yd, ws, costs, loss, one, 0, gx, pipe=pipe, groups=args.groups,
+                           global_ids=ids_dev, n_global=B_global, cost_vector=vec)
+            dist.all_reduce(vec, op=dist.ReduceOp.SUM)
 
     def fence():
         if world > 1:
@@ -337,23 +346,32 @@ def main():
     if st[0] & 0x3:
         raise SystemExit(f"device status reports invalid inputs: {st}")
 
-    # ---- timed region: CUDA events on the launching stream, per-step marks for the kernel breakdown
+    # ---- timed region: K pipelined steps between two CUDA events on the launching stream (every side stream is
+    # joined back into it inside the call)
     K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local) if rank == 0 else None
     fence()
     mark = sampler.mark() if sampler else 0
+    begin.record()
+    for k in range(K):
+        step()
+    end.record()
+    fence()
+    clocks = sampler.stop(mark) if sampler else None
+    total_ms = begin.elapsed_time(end)
+    loss_value = float(vec[B_global] if world > 1 else loss)
+
+    # ---- kernel breakdown: the same work as two plain calls (no overlap), so that the gradient kernel - one launch
+    # over the whole matrix - can be timed by itself for the roofline
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
     for k in range(K):
         ev[k][0].record()
         forward()
         ev[k][1].record()
         capi.backward(p, x, lxd, lyd, yd, ws, one, 0, gx)
         ev[k][2].record()
-    end = torch.cuda.Event(enable_timing=True)
-    end.record()
     fence()
-    clocks = sampler.stop(mark) if sampler else None
-    total_ms = ev[0][0].elapsed_time(end)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
     t = torch.tensor([total_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
@@ -362,7 +380,6 @@ def main():
     total_ms, fwd_ms, bwd_ms = [float(v) for v in t.cpu()]
     ms_per_step = total_ms / K
     value = nodes_global / (ms_per_step * 1e-3)
-    loss_value = float(vec[B_global] if world > 1 else loss)
 
     # ---- end to end through the host-buffer entry point: pinned host logits in, host gradients + costs out
     e2e = None
@@ -418,13 +435,19 @@ def main():
                    "logits_bytes_per_gpu": int(x_host.numel() * elt), "sharding": f"lattice-size LPT over {world} rank(s)",
                    "l2": "inputs larger than L2 (no flush needed)", "reduction": wl.reduction,
                    "shard_imbalance": round(sharding.shard_imbalance(lx, ly, plan), 4)},
-        "gpu_launches": 4 * K,
-        "kernels_per_step": ["prep_kernel", "gather_rows_kernel", "wavefront_split_kernel", "grad_rows_kernel"],
-        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "loss": loss_value,
+        "gpu_launches": (1 + 3 * n_groups) * K,
+        "kernels_per_step": ["prep_kernel"] + ["gather_rows_kernel", "wavefront_split_kernel",
+                                               "grad_rows_kernel"] * n_groups,
+        "pipeline": {"entry": "cwrnnt_loss_grad", "sequence_groups": n_groups,
+                     "unpipelined_ms_per_step": fwd_ms + bwd_ms, "unpipelined_fwd_ms": fwd_ms,
+                     "unpipelined_bwd_ms": bwd_ms},
+        "loss": loss_value,
         "roofline": {"bound": "hbm", "kernel": "grad_rows_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                      "traffic": traffic * nodes_local if traffic else None,
-                     "algorithmic_bytes": grad_bytes, "launch_ms": bwd_ms},
+                     "algorithmic_bytes": grad_bytes, "launch_ms": bwd_ms,
+                     "timed": "one launch over the whole matrix (cwrnnt_backward), CUDA events, mean of the "
+                              "breakdown loop that follows the timed region"},
         "step_roofline": {"achieved": 3.0 * nodes_local * wl.V * elt / (ms_per_step * 1e-3) / 1e9, "peak": peak,
                           "unit": "GB/s", "frac": 3.0 * nodes_local * wl.V * elt / (ms_per_step * 1e-3) / 1e9 / peak,
                           "bytes_per_node": 3 * wl.V * elt},

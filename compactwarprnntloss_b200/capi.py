@@ -26,7 +26,8 @@ EXPORTS = [
     "cwrnnt_backward", "cwrnnt_pair_grads", "cwrnnt_export_alpha_beta", "cwrnnt_scatter_scratch_bytes",
     "cwrnnt_scatter_backward", "cwrnnt_read_status", "cwrnnt_host_ctx_create", "cwrnnt_host_ctx_destroy",
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
-    "cwrnnt_pack_padded", "cwrnnt_unpack_padded",
+    "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
+    "cwrnnt_scale_grad", "cwrnnt_pipeline_groups",
 ]
 
 
@@ -61,6 +62,13 @@ def lib():
         L.cwrnnt_forward.argtypes = [pp, vp, vp, vp, vp, vp, i64, vp, vp, vp]
         L.cwrnnt_forward_sharded.argtypes = [pp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp, vp]
         L.cwrnnt_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
+        L.cwrnnt_pipe_create.argtypes = [ctypes.POINTER(vp)]
+        L.cwrnnt_pipe_destroy.argtypes = [vp]
+        L.cwrnnt_pipe_destroy.restype = None
+        L.cwrnnt_loss_grad.argtypes = [vp, pp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp, vp, i32, vp, i32, vp]
+        L.cwrnnt_scale_grad.argtypes = [pp, vp, vp, vp]
+        L.cwrnnt_pipeline_groups.restype = i32
+        L.cwrnnt_pipeline_groups.argtypes = [pp, i32]
         L.cwrnnt_pair_grads.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_export_alpha_beta.argtypes = [pp, vp, vp, vp, i32, i32, vp, vp, vp]
         L.cwrnnt_scatter_scratch_bytes.restype = i64
@@ -145,6 +153,54 @@ def backward(p: Problem, x, lx, ly, y, workspace, grad_costs, grad_costs_stride,
         check(lib().cwrnnt_backward(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
                                     _ptr(grad_costs), grad_costs_stride, _ptr(grad_x), _stream(x.device)),
               "cwrnnt_backward")
+
+
+class Pipe:
+    """Side streams and events of the pipelined step (cwrnnt_pipe_create); bound to one device, one call at a time."""
+
+    def __init__(self, device):
+        self.device = torch.device("cuda", device) if not isinstance(device, torch.device) else device
+        self._h = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream()  # make sure the primary context exists
+            check(lib().cwrnnt_pipe_create(ctypes.byref(self._h)), "cwrnnt_pipe_create")
+
+    def close(self):
+        if self._h:
+            lib().cwrnnt_pipe_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def loss_grad(p: Problem, x, lx, ly, y, workspace, costs, loss, grad_costs, grad_costs_stride, grad_x, pipe=None,
+              groups=0, global_ids=None, n_global=0, cost_vector=None) -> None:
+    """Costs, loss and gradient in one call (cwrnnt_loss_grad): with a Pipe, the wavefront of each sequence group
+    runs on a side stream underneath the gather and gradient passes; without, the same work on the current stream."""
+    with torch.cuda.device(x.device):
+        check(lib().cwrnnt_loss_grad(pipe._h if pipe is not None else None, ctypes.byref(p), _ptr(x), _ptr(lx),
+                                     _ptr(ly), _ptr(y), _ptr(workspace), workspace.numel(), _ptr(costs), _ptr(loss),
+                                     _ptr(grad_costs), grad_costs_stride, _ptr(grad_x), _ptr(global_ids), n_global,
+                                     _ptr(cost_vector), groups, _stream(x.device)), "cwrnnt_loss_grad")
+
+
+def pipeline_groups(p: Problem, groups: int = 0) -> int:
+    """Sequence groups a pipelined step of this problem runs with (1 + 3 * groups kernel launches)."""
+    n = lib().cwrnnt_pipeline_groups(ctypes.byref(p), groups)
+    if n < 0:
+        raise CwrnntError("cwrnnt_pipeline_groups: invalid argument")
+    return n
+
+
+def scale_grad(p: Problem, grad_x, factor) -> None:
+    """grad_x *= factor[0] in place (factor: device scalar of the costs dtype); free on the device when it is 1."""
+    with torch.cuda.device(grad_x.device):
+        check(lib().cwrnnt_scale_grad(ctypes.byref(p), _ptr(grad_x), _ptr(factor), _stream(grad_x.device)),
+              "cwrnnt_scale_grad")
 
 
 def pair_grads(p: Problem, x, lx, ly, y, workspace, grads) -> None:

@@ -1,15 +1,48 @@
 // C ABI of the engine (include/cwarp_rnnt_b200.h): argument checks, workspace carving, kernel sequencing.
-// No allocation, no synchronisation (except cwrnnt_read_status), no exceptions.
+// No device allocation, no synchronisation (except cwrnnt_read_status), no exceptions; cwrnnt_pipe_create owns the
+// only resources made here (side streams and events).
 #include <cstdio>
 #include <cstring>
+#include <new>
 
 #include "cwrnnt_kernels.h"
 
 using namespace cwrnnt;
 
+// Side streams and events of a pipelined step (cwrnnt_loss_grad).
+struct cwrnnt_pipe {
+    int device;
+    cudaStream_t alt;                  // second stream of the streaming kernels (odd groups; even ones use the caller's)
+    cudaStream_t side[kMaxGroups];     // highest priority: the wavefront of group g
+    cudaEvent_t gathered[kMaxGroups];  // recorded after the gather of range g
+    cudaEvent_t solved[kMaxGroups];    // recorded on side[g] after the wavefront of group g
+    cudaEvent_t forked, joined;        // caller's stream -> alt at the start, alt -> caller's stream at the end
+};
+
 namespace {
 
+int64_t elt_bytes(int dtype) { return dtype == CWRNNT_F32 ? 4 : (dtype == CWRNNT_F64 ? 8 : 2); }
+
 thread_local char g_last_error[256] = "";
+
+// Sequence groups of a pipelined step. Enough of them that the first wavefront starts early and the last one has
+// gradient work to hide under, few enough that the streaming launches stay large (each ends in a partly filled wave).
+GroupPlan plan_groups(const cwrnnt_problem &p, int groups)
+{
+    const int64_t bytes = p.n_rows * int64_t(p.V) * elt_bytes(p.dtype);
+    // measured on B200: 4 groups for a large batch of ordinary sequences (32 x [200 x 50] x 1024 fp32: 0.592 ms against
+    // 0.628 unpipelined, 0.607 with 2, 0.609 with 8); 8 when the batch is a handful of long sequences, whose
+    // wavefronts are the critical path (4 x [1250 x 300] x 512: 1.48 ms against 1.85, 1.64 with 4)
+    const int large = p.B <= 8 ? 8 : 4;
+    const int want = groups > 0 ? groups : (bytes >= (int64_t(256) << 20) ? large : (bytes >= (int64_t(32) << 20) ? 2 : 1));
+    const int64_t kAlign = 2048;  // whole tiles of every row shape of the streaming kernels
+    GroupPlan plan{1, p.n_rows > 0 ? p.n_rows : 1};
+    if (want > 1 && p.n_rows > kAlign) {
+        plan.range_rows = align_up((p.n_rows + want - 1) / want, kAlign);
+        plan.count = int((p.n_rows + plan.range_rows - 1) / plan.range_rows);
+    }
+    return plan;
+}
 
 int fail_launch(const char *what, cudaError_t e)
 {
@@ -121,6 +154,137 @@ int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, c
     cudaError_t e = launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x,
                                 reinterpret_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? CWRNNT_OK : fail_launch("grad", e);
+}
+
+int cwrnnt_pipe_create(cwrnnt_pipe **out)
+{
+    if (!out) return CWRNNT_ERR_ARGUMENT;
+    *out = nullptr;
+    cwrnnt_pipe *pipe = new (std::nothrow) cwrnnt_pipe{};
+    if (!pipe) return CWRNNT_ERR_LAUNCH;
+    int least = 0, greatest = 0;
+    cudaError_t e = cudaGetDevice(&pipe->device);
+    if (e == cudaSuccess) e = cudaDeviceGetStreamPriorityRange(&least, &greatest);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&pipe->alt, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->forked, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->joined, cudaEventDisableTiming);
+    for (int g = 0; g < kMaxGroups && e == cudaSuccess; ++g) {
+        // highest priority: a wavefront CTA must get onto an SM as soon as a CTA of the streaming kernels retires
+        e = cudaStreamCreateWithPriority(&pipe->side[g], cudaStreamNonBlocking, greatest);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->gathered[g], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->solved[g], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) {
+        fail_launch("pipe_create", e);
+        cwrnnt_pipe_destroy(pipe);
+        return CWRNNT_ERR_LAUNCH;
+    }
+    *out = pipe;
+    return CWRNNT_OK;
+}
+
+void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe)
+{
+    if (!pipe) return;
+    if (pipe->alt) cudaStreamDestroy(pipe->alt);
+    if (pipe->forked) cudaEventDestroy(pipe->forked);
+    if (pipe->joined) cudaEventDestroy(pipe->joined);
+    for (int g = 0; g < kMaxGroups; ++g) {
+        if (pipe->side[g]) cudaStreamDestroy(pipe->side[g]);
+        if (pipe->gathered[g]) cudaEventDestroy(pipe->gathered[g]);
+        if (pipe->solved[g]) cudaEventDestroy(pipe->solved[g]);
+    }
+    delete pipe;
+}
+
+int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly,
+                     const int32_t *y, void *workspace, int64_t workspace_bytes, void *costs, void *loss,
+                     const void *grad_costs, int32_t grad_costs_stride, void *grad_x, const int32_t *global_ids,
+                     int32_t n_global, void *cost_vector, int32_t groups, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->flags & CWRNNT_COSTS_ONLY) return CWRNNT_ERR_ARGUMENT;
+    if (groups < 0 || groups > kMaxGroups) return CWRNNT_ERR_ARGUMENT;
+    if (grad_costs_stride != 0 && grad_costs_stride != 1) return CWRNNT_ERR_ARGUMENT;
+    if (cost_vector ? n_global < p->B : (global_ids != nullptr || n_global != 0)) return CWRNNT_ERR_ARGUMENT;
+    if (p->B == 0) return CWRNNT_OK;
+    if (!lx || !ly || !costs || (p->n_rows > 0 && (!x || !grad_x)) || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, workspace_bytes, &w);
+    if (st) return st;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (pipe) {
+        int device = -1;
+        if ((e = cudaGetDevice(&device)) != cudaSuccess) return fail_launch("loss_grad", e);
+        if (device != pipe->device) return CWRNNT_ERR_ARGUMENT;
+    }
+
+    const GroupPlan plan = plan_groups(*p, pipe ? groups : 1);
+    const int G = plan.count;
+    ShardOutput shard{global_ids, n_global, cost_vector};
+
+    // Streams. The streaming kernels of consecutive groups alternate between the caller's stream and pipe->alt: two
+    // launches on one stream leave the SMs idle between the last CTAs of one and the first of the next, on two
+    // streams the next one's CTAs fill in as the previous one's run out (they touch different rows). The wavefront
+    // of group g runs on the high-priority stream side[g].
+#define CWRNNT_TRY(call, what) \
+    if ((e = (call)) != cudaSuccess) return fail_launch(what, e)
+    auto rows_stream = [&](int g) { return (G > 1 && (g & 1)) ? pipe->alt : s; };
+    CWRNNT_TRY(launch_prep(*p, lx, ly, w, costs, s, plan), "prep");
+    if (G > 1) {
+        CWRNNT_TRY(cudaEventRecord(pipe->forked, s), "event");
+        CWRNNT_TRY(cudaStreamWaitEvent(pipe->alt, pipe->forked, 0), "event");
+    }
+    for (int g = 0; g < G; ++g) {
+        const int64_t row0 = g * plan.range_rows;
+        const int64_t row1 = g == G - 1 ? p->n_rows : row0 + plan.range_rows;
+        CWRNNT_TRY(launch_gather(*p, x, lx, ly, y, w, rows_stream(g), row0, row1), "gather");
+        cudaStream_t k2 = G > 1 ? pipe->side[g] : s;
+        if (G > 1) {
+            // group g needs ranges 0..g: the gathers of g, g-2, .. precede this record on its stream, those of
+            // g-1, g-3, .. precede the record of g-1 on the other one
+            CWRNNT_TRY(cudaEventRecord(pipe->gathered[g], rows_stream(g)), "event");
+            CWRNNT_TRY(cudaStreamWaitEvent(k2, pipe->gathered[g], 0), "event");
+            if (g > 0) CWRNNT_TRY(cudaStreamWaitEvent(k2, pipe->gathered[g - 1], 0), "event");
+        }
+        CWRNNT_TRY(launch_wavefront(*p, lx, ly, w, costs, loss, cost_vector ? &shard : nullptr, k2, plan, g),
+                   "wavefront");
+        if (G > 1) CWRNNT_TRY(cudaEventRecord(pipe->solved[g], k2), "event");
+    }
+    for (int g = 0; g < G; ++g) {
+        GradRows span{nullptr, 0};
+        if (G > 1) {
+            CWRNNT_TRY(cudaStreamWaitEvent(rows_stream(g), pipe->solved[g], 0), "event");
+            // a group holds the sequences that END in its range, so it is about one range long, give or take a
+            // sequence: the grid is sized for one range and a longer group is finished by the same CTAs
+            span = GradRows{w.bounds + g, plan.range_rows};
+        }
+        CWRNNT_TRY(launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x, rows_stream(g), span),
+                   "grad");
+    }
+    if (G > 1) {
+        CWRNNT_TRY(cudaEventRecord(pipe->joined, pipe->alt), "event");
+        CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->joined, 0), "event");
+    }
+#undef CWRNNT_TRY
+    return CWRNNT_OK;
+}
+
+int32_t cwrnnt_pipeline_groups(const cwrnnt_problem *p, int32_t groups)
+{
+    if (check_problem(p) != CWRNNT_OK || groups < 0 || groups > kMaxGroups) return -1;
+    return plan_groups(*p, groups).count;
+}
+
+int cwrnnt_scale_grad(const cwrnnt_problem *p, void *grad_x, const void *factor, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (!factor || (p->n_rows > 0 && !grad_x)) return CWRNNT_ERR_ARGUMENT;
+    cudaError_t e = launch_scale(*p, grad_x, factor, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("scale_grad", e);
 }
 
 int cwrnnt_pair_grads(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,

@@ -12,10 +12,23 @@
 namespace cwrnnt {
 
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; persistent grids are sized in multiples of this
+constexpr int kMaxGroups = 8;  // sequence groups of a pipelined step (cwrnnt_loss_grad)
+
+// Pipelined step: the rows are cut into `count` nominal ranges of `range_rows` rows; a sequence belongs to the group
+// of the range that holds its LAST row, so group g is complete as soon as ranges 0..g have been gathered.
+struct GroupPlan {
+    int count;           // 1 = no grouping
+    int64_t range_rows;  // rows per nominal range (the last range may be shorter)
+};
+__host__ __device__ inline int group_of_row(int64_t row, const GroupPlan &plan)
+{
+    const int64_t g = row / plan.range_rows;
+    return int(g < plan.count - 1 ? g : plan.count - 1);
+}
 
 // ------------------------------------------------------------------------------------------------ workspace
 // One caller-provided allocation, carved deterministically from (n_rows, B) so forward and backward agree.
-//   header   : 4 status words + completion ticket
+//   header   : 4 status words + completion ticket + row bounds of the sequence groups of a pipelined step
 //   off      : int64 [B+1]   exclusive prefix sum of T_n*(U_n+1) (row offset of each sequence)
 //   order    : int32 [B]     sequences by descending T_n+U_n (wavefront critical path), longest first
 //   ll_alpha : double [B]    alpha(T-1,U) + blank(T-1,U)
@@ -28,6 +41,7 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; persistent grids are siz
 struct Workspace {
     int32_t *status;
     unsigned int *ticket;
+    int64_t *bounds;  // [kMaxGroups + 1] first row of each sequence group, then n_rows (written by K0)
     int64_t *off;
     int32_t *order;
     double *ll_alpha;
@@ -51,7 +65,7 @@ __host__ inline int64_t carve_workspace(int64_t n_rows, int32_t B, void *base, W
         return here;
     };
     const int64_t rows = n_rows > 0 ? n_rows : 1;
-    int64_t o_hdr = take(64);
+    int64_t o_hdr = take(256);
     int64_t o_off = take(8 * (int64_t(B) + 1));
     int64_t o_ord = take(4 * int64_t(B));
     int64_t o_lla = take(8 * int64_t(B));
@@ -65,6 +79,7 @@ __host__ inline int64_t carve_workspace(int64_t n_rows, int32_t B, void *base, W
         char *b = static_cast<char *>(base);
         w->status = reinterpret_cast<int32_t *>(b + o_hdr);
         w->ticket = reinterpret_cast<unsigned int *>(b + o_hdr + 16);
+        w->bounds = reinterpret_cast<int64_t *>(b + o_hdr + 64);
         w->off = reinterpret_cast<int64_t *>(b + o_off);
         w->order = reinterpret_cast<int32_t *>(b + o_ord);
         w->ll_alpha = reinterpret_cast<double *>(b + o_lla);

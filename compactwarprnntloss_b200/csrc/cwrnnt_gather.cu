@@ -16,7 +16,7 @@ namespace cwrnnt {
 // FULL: the row fills all LPR*NV vector slots (no per-vector predicate).
 template <typename T, int LPR, int NV, bool FULL>
 __global__ void __launch_bounds__(kStreamThreads)
-gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const int32_t *__restrict__ lx,
+gather_rows_kernel(const T *__restrict__ x, int V, RowRange rows, int B, const int32_t *__restrict__ lx,
                    const int32_t *__restrict__ ly, const int32_t *__restrict__ y, int y_stride, int blank,
                    Workspace w, int run_len)
 {
@@ -31,61 +31,67 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
     // A CTA covers GPC * run_len consecutive rows: lane group g takes the run_len rows starting at
     // (blockIdx.x * GPC + g) * run_len. The grid is NOT persistent - one such tile per CTA, dispatched in order by
     // the hardware, so that the CTAs in flight sweep the matrix as one front (measured: 15 % more bandwidth than a
-    // persistent grid-stride loop on this access pattern).
-    const int64_t first = (int64_t(blockIdx.x) * GPC + threadIdx.x / LPR) * run_len;
-    const int64_t limit = first + run_len < n_rows ? first + run_len : n_rows;
+    // persistent grid-stride loop on this access pattern). Only a range whose length the host did not know can be
+    // longer than the grid; its CTAs then carry on with the tile gridDim.x further.
+    int64_t r_begin, r_end;
+    rows.resolve(r_begin, r_end);
+    const int64_t tile_rows = int64_t(GPC) * run_len;
     bool any_bad = false;
 
     RowWalker rw;
-    for (int i = 0; i < run_len; ++i) {  // same trip count for every group of the warp (shuffles below)
-        const int64_t r = first + i;
-        const bool live = r < limit;
-        uint4 v[NV];
-        A xb = A(0), xl = A(0);
-        int label = -1;
-        if (live) {
-            if (i == 0) rw.start(r, w.off, B, lx, ly);
-            const T *row = x + r * int64_t(V);
-            const uint4 *rv = reinterpret_cast<const uint4 *>(row);
+    for (int64_t tile = r_begin + blockIdx.x * tile_rows; tile < r_end; tile += gridDim.x * tile_rows) {
+        const int64_t first = tile + (threadIdx.x / LPR) * run_len;
+        const int64_t limit = first + run_len < r_end ? first + run_len : r_end;
+        for (int i = 0; i < run_len; ++i) {  // same trip count for every group of the warp (shuffles below)
+            const int64_t r = first + i;
+            const bool live = r < limit;
+            uint4 v[NV];
+            A xb = A(0), xl = A(0);
+            int label = -1;
+            if (live) {
+                if (i == 0) rw.start(r, w.off, B, lx, ly);
+                const T *row = x + r * int64_t(V);
+                const uint4 *rv = reinterpret_cast<const uint4 *>(row);
 #pragma unroll
-            for (int j = 0; j < NV; ++j)
-                if (FULL || j * LPR + gl < nvec) v[j] = ld_nc(rv + j * LPR + gl);
-            label = rw.label(y, y_stride, V, any_bad);
-            xb = E::to_acc(__ldg(row + blank));
-            if (label >= 0) xl = E::to_acc(__ldg(row + label));
-        }
-        A mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            if (live && (FULL || j * LPR + gl < nvec)) {
-                A e[VE];
-                E::unpack(v[j], e);
-#pragma unroll
-                for (int c = 0; c < VE; ++c) mx = e[c] > mx ? e[c] : mx;
+                for (int j = 0; j < NV; ++j)
+                    if (FULL || j * LPR + gl < nvec) v[j] = ld_nc(rv + j * LPR + gl);
+                label = rw.label(y, y_stride, V, any_bad);
+                xb = E::to_acc(__ldg(row + blank));
+                if (label >= 0) xl = E::to_acc(__ldg(row + label));
             }
-        }
-        mx = group_max<LPR>(mx);
-        const RowShift<A> shift(mx);
-        A sum = A(0);
+            A mx = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            if (live && (FULL || j * LPR + gl < nvec)) {
-                A e[VE];
-                E::unpack(v[j], e);
+            for (int j = 0; j < NV; ++j) {
+                if (live && (FULL || j * LPR + gl < nvec)) {
+                    A e[VE];
+                    E::unpack(v[j], e);
 #pragma unroll
-                for (int c = 0; c < VE; ++c) sum += shift.term(e[c]);
+                    for (int c = 0; c < VE; ++c) mx = e[c] > mx ? e[c] : mx;
+                }
             }
-        }
-        sum = group_sum<LPR>(sum);
-        if (live) {
-            if (gl == 0) {
-                const double lse = shift.lse(sum);
-                const int64_t at = rw.off + rw.at;
-                w.lse[r] = lse;
-                w.lp_blank[at] = double(xb) - lse;
-                if (label >= 0) w.lp_label[at] = double(xl) - lse;
+            mx = group_max<LPR>(mx);
+            const RowShift<A> shift(mx);
+            A sum = A(0);
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                if (live && (FULL || j * LPR + gl < nvec)) {
+                    A e[VE];
+                    E::unpack(v[j], e);
+#pragma unroll
+                    for (int c = 0; c < VE; ++c) sum += shift.term(e[c]);
+                }
             }
-            rw.advance(w.off, B, lx, ly);
+            sum = group_sum<LPR>(sum);
+            if (live) {
+                if (gl == 0) {
+                    const double lse = shift.lse(sum);
+                    const int64_t at = rw.off + rw.at;
+                    w.lse[r] = lse;
+                    w.lp_blank[at] = double(xb) - lse;
+                    if (label >= 0) w.lp_label[at] = double(xl) - lse;
+                }
+                rw.advance(w.off, B, lx, ly);
+            }
         }
     }
     if (any_bad) atomicOr(w.status, CWRNNT_ST_BAD_LABEL);
@@ -94,7 +100,7 @@ gather_rows_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
 // Any V, any alignment: one warp per row, two coalesced scalar passes (the second hits L1/L2).
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
-gather_rows_generic_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const int32_t *__restrict__ lx,
+gather_rows_generic_kernel(const T *__restrict__ x, int V, RowRange rows, int B, const int32_t *__restrict__ lx,
                            const int32_t *__restrict__ ly, const int32_t *__restrict__ y, int y_stride, int blank,
                            Workspace w)
 {
@@ -102,10 +108,12 @@ gather_rows_generic_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B
     using A = typename E::acc;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
     const int lane = threadIdx.x & 31;
+    int64_t row0, row1;
+    rows.resolve(row0, row1);
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
-    const int64_t r_begin = ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
-    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
+    const int64_t per_warp = (row1 - row0 + n_warps - 1) / n_warps;
+    const int64_t r_begin = row0 + ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
+    const int64_t r_end = r_begin + per_warp < row1 ? r_begin + per_warp : row1;
     bool any_bad = false;
     RowWalker rw;
     if (r_begin < r_end) rw.start(r_begin, w.off, B, lx, ly);
@@ -137,7 +145,7 @@ gather_rows_generic_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B
 // Log-probability input (the reference contract): no normalisation, two elements per row, one thread per row run.
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
-gather_pair_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const int32_t *__restrict__ lx,
+gather_pair_kernel(const T *__restrict__ x, int V, RowRange rows, int B, const int32_t *__restrict__ lx,
                    const int32_t *__restrict__ ly, const int32_t *__restrict__ y, int y_stride, int blank,
                    Workspace w)
 {
@@ -146,8 +154,10 @@ gather_pair_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
     bool any_bad = false;
     // consecutive threads take consecutive rows (the two 8-byte results per row then coalesce per warp); each thread
     // strides by the grid size, so its position is re-located per row
+    int64_t row0, row1;
+    rows.resolve(row0, row1);
     const int64_t stride = int64_t(gridDim.x) * kStreamThreads;
-    for (int64_t r = int64_t(blockIdx.x) * kStreamThreads + threadIdx.x; r < n_rows; r += stride) {
+    for (int64_t r = row0 + int64_t(blockIdx.x) * kStreamThreads + threadIdx.x; r < row1; r += stride) {
         RowWalker rw;
         rw.start(r, w.off, B, lx, ly);
         const int label = rw.label(y, y_stride, V, any_bad);
@@ -162,14 +172,16 @@ gather_pair_kernel(const T *__restrict__ x, int V, int64_t n_rows, int B, const 
 
 template <typename T>
 static cudaError_t launch_gather_t(const cwrnnt_problem &p, const T *x, const int32_t *lx, const int32_t *ly,
-                                   const int32_t *y, const Workspace &w, cudaStream_t s)
+                                   const int32_t *y, const Workspace &w, cudaStream_t s, int64_t row0, int64_t row1)
 {
-    if (p.n_rows == 0) return cudaSuccess;
+    if (row1 <= row0) return cudaSuccess;
+    const int64_t n_rows = row1 - row0;
+    const RowRange rows{row0, row1, nullptr};
     constexpr int VE = Elt<T>::VE;
     if (!(p.flags & CWRNNT_FUSED_LOG_SOFTMAX)) {
-        const int64_t tiles = (p.n_rows + kStreamThreads - 1) / kStreamThreads;
+        const int64_t tiles = (n_rows + kStreamThreads - 1) / kStreamThreads;
         const int grid = int(tiles < kNumSMs * 8 ? tiles : kNumSMs * 8);
-        gather_pair_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, w);
+        gather_pair_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank, w);
         return cudaGetLastError();
     }
     RowShape shape{};
@@ -183,9 +195,9 @@ static cudaError_t launch_gather_t(const cwrnnt_problem &p, const T *x, const in
         const int run_len = int64_t(p.V) * int64_t(sizeof(T)) >= 8192 ? 16 : 8;
 #define LAUNCH(LPR, NV, FULL)                                                                                      \
     {                                                                                                              \
-        const unsigned grid = tiled_grid(p.n_rows, int64_t(kStreamThreads / LPR) * run_len);                       \
+        const unsigned grid = tiled_grid(n_rows, int64_t(kStreamThreads / LPR) * run_len);                         \
         gather_rows_kernel<T, LPR, NV, FULL><<<grid, kStreamThreads, 0, s>>>(                                      \
-            x, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, w, run_len);                                    \
+            x, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank, w, run_len);                                        \
     }
 #define CALL(LPR, NV)                    \
     {                                    \
@@ -196,21 +208,22 @@ static cudaError_t launch_gather_t(const cwrnnt_problem &p, const T *x, const in
 #undef CALL
 #undef LAUNCH
     } else {
-        const unsigned grid = tiled_grid(p.n_rows, 8 * 4);  // 8 warps, 4 rows each
-        gather_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
+        const unsigned grid = tiled_grid(n_rows, 8 * 4);  // 8 warps, 4 rows each
+        gather_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, rows, p.B, lx, ly, y, p.y_stride,
                                                                       p.blank, w);
     }
     return cudaGetLastError();
 }
 
 cudaError_t launch_gather(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
-                          const int32_t *y, const Workspace &w, cudaStream_t s)
+                          const int32_t *y, const Workspace &w, cudaStream_t s, int64_t row0, int64_t row1)
 {
+    if (row1 < 0) row1 = p.n_rows;
     switch (p.dtype) {
-    case CWRNNT_F32: return launch_gather_t(p, static_cast<const float *>(x), lx, ly, y, w, s);
-    case CWRNNT_F16: return launch_gather_t(p, static_cast<const __half *>(x), lx, ly, y, w, s);
-    case CWRNNT_BF16: return launch_gather_t(p, static_cast<const __nv_bfloat16 *>(x), lx, ly, y, w, s);
-    case CWRNNT_F64: return launch_gather_t(p, static_cast<const double *>(x), lx, ly, y, w, s);
+    case CWRNNT_F32: return launch_gather_t(p, static_cast<const float *>(x), lx, ly, y, w, s, row0, row1);
+    case CWRNNT_F16: return launch_gather_t(p, static_cast<const __half *>(x), lx, ly, y, w, s, row0, row1);
+    case CWRNNT_BF16: return launch_gather_t(p, static_cast<const __nv_bfloat16 *>(x), lx, ly, y, w, s, row0, row1);
+    case CWRNNT_F64: return launch_gather_t(p, static_cast<const double *>(x), lx, ly, y, w, s, row0, row1);
     }
     return cudaErrorInvalidValue;
 }

@@ -49,7 +49,7 @@ __device__ __forceinline__ void row_terms(const RowWalker &rw, const Workspace &
 // evict-first variants measured 7 % slower.
 template <typename T, int LPR, int NV, bool FULL>
 __global__ void __launch_bounds__(kStreamThreads)
-grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_rows, int B,
+grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange rows, int B,
                  const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, const int32_t *__restrict__ y,
                  int y_stride, int blank, int flags, double mean_inv, Workspace w,
                  const typename Elt<T>::cost *__restrict__ grad_costs, int gc_stride, int run_len)
@@ -63,56 +63,62 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_r
 
     const int gl = threadIdx.x % LPR;
     const int nvec = V / VE;
-    // A CTA covers GPC * run_len consecutive rows, one such tile per CTA (non-persistent grid, see the gather kernel).
-    const int64_t first = (int64_t(blockIdx.x) * GPC + threadIdx.x / LPR) * run_len;
-    const int64_t limit = first + run_len < n_rows ? first + run_len : n_rows;
+    // A CTA covers GPC * run_len consecutive rows, one such tile per CTA (non-persistent grid, see the gather kernel);
+    // it carries on gridDim.x tiles further only when the range (known on the device alone) outgrew the grid.
+    int64_t r_begin, r_end;
+    rows.resolve(r_begin, r_end);
+    const int64_t tile_rows = int64_t(GPC) * run_len;
     bool ignored = false;
 
     RowWalker rw;
-    for (int64_t r = first; r < limit; ++r) {
-        if (r == first) rw.start(r, w.off, B, lx, ly);
-        const T *row = x + r * int64_t(V);
-        T *orow = gx + r * int64_t(V);
-        const uint4 *rv = reinterpret_cast<const uint4 *>(row);
-        uint4 *ov = reinterpret_cast<uint4 *>(orow);
-        uint4 v[NV];
+    for (int64_t tile = r_begin + blockIdx.x * tile_rows; tile < r_end; tile += gridDim.x * tile_rows) {
+        const int64_t first = tile + (threadIdx.x / LPR) * run_len;
+        const int64_t limit = first + run_len < r_end ? first + run_len : r_end;
+        for (int64_t r = first; r < limit; ++r) {
+            if (r == first) rw.start(r, w.off, B, lx, ly);
+            const T *row = x + r * int64_t(V);
+            T *orow = gx + r * int64_t(V);
+            const uint4 *rv = reinterpret_cast<const uint4 *>(row);
+            uint4 *ov = reinterpret_cast<uint4 *>(orow);
+            uint4 v[NV];
 #pragma unroll
-        for (int j = 0; j < NV; ++j)
-            if (FULL || j * LPR + gl < nvec) v[j] = ld_nc(rv + j * LPR + gl);
-        const int label = rw.label(y, y_stride, V, ignored);
-        const A xb = E::to_acc(__ldg(row + blank));
-        const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
-        const double lse = __ldg(w.lse + r);
-        double wb, wl;
-        row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
-        const A tot = A(wb + wl);
-        const A lse_a = A(lse);
+            for (int j = 0; j < NV; ++j)
+                if (FULL || j * LPR + gl < nvec) v[j] = ld_nc(rv + j * LPR + gl);
+            const int label = rw.label(y, y_stride, V, ignored);
+            const A xb = E::to_acc(__ldg(row + blank));
+            const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
+            const double lse = __ldg(w.lse + r);
+            double wb, wl;
+            row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
+            const A tot = A(wb + wl);
+            const A lse_a = A(lse);
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            if (FULL || j * LPR + gl < nvec) {
-                A e[VE];
-                E::unpack(v[j], e);
+            for (int j = 0; j < NV; ++j) {
+                if (FULL || j * LPR + gl < nvec) {
+                    A e[VE];
+                    E::unpack(v[j], e);
 #pragma unroll
-                for (int c = 0; c < VE; ++c) e[c] = exp_shifted(e[c], lse_a) * tot;
-                ov[j * LPR + gl] = E::pack(e);
+                    for (int c = 0; c < VE; ++c) e[c] = exp_shifted(e[c], lse_a) * tot;
+                    ov[j * LPR + gl] = E::pack(e);
+                }
             }
+            // the two sparse corrections, by the lane that stored the enclosing vector (same-thread program order)
+            if ((blank / VE) % LPR == gl) {
+                A gb = exp_shifted(xb, lse_a) * tot - A(wb);
+                if (label == blank) gb -= A(wl);
+                orow[blank] = E::from_acc(gb);
+            }
+            if (label >= 0 && label != blank && (label / VE) % LPR == gl)
+                orow[label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
+            rw.advance(w.off, B, lx, ly);
         }
-        // the two sparse corrections, by the lane that stored the enclosing vector (same-thread program order)
-        if ((blank / VE) % LPR == gl) {
-            A gb = exp_shifted(xb, lse_a) * tot - A(wb);
-            if (label == blank) gb -= A(wl);
-            orow[blank] = E::from_acc(gb);
-        }
-        if (label >= 0 && label != blank && (label / VE) % LPR == gl)
-            orow[label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
-        rw.advance(w.off, B, lx, ly);
     }
 }
 
 // Any V / alignment, logits mode: one warp per row, scalar coalesced accesses.
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
-grad_rows_generic_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_rows, int B,
+grad_rows_generic_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange rows, int B,
                          const int32_t *__restrict__ lx, const int32_t *__restrict__ ly,
                          const int32_t *__restrict__ y, int y_stride, int blank, int flags, double mean_inv,
                          Workspace w, const typename Elt<T>::cost *__restrict__ grad_costs, int gc_stride)
@@ -122,10 +128,12 @@ grad_rows_generic_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int
     using CostT = typename E::cost;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
     const int lane = threadIdx.x & 31;
+    int64_t row0, row1;
+    rows.resolve(row0, row1);
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
-    const int64_t r_begin = ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
-    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
+    const int64_t per_warp = (row1 - row0 + n_warps - 1) / n_warps;
+    const int64_t r_begin = row0 + ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
+    const int64_t r_end = r_begin + per_warp < row1 ? r_begin + per_warp : row1;
     if (r_begin >= r_end) return;
     bool ignored = false;
     RowWalker rw;
@@ -153,7 +161,7 @@ grad_rows_generic_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int
 // Log-prob mode: zeros and the two sparse terms; the input is only touched at two elements per row.
 template <typename T>
 __global__ void __launch_bounds__(kStreamThreads)
-grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int64_t n_rows, int B,
+grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange rows, int B,
                         const int32_t *__restrict__ lx, const int32_t *__restrict__ ly,
                         const int32_t *__restrict__ y, int y_stride, int blank, int flags, double mean_inv,
                         Workspace w, const typename Elt<T>::cost *__restrict__ grad_costs, int gc_stride, int vec_ok)
@@ -164,10 +172,12 @@ grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int6
     constexpr int VE = E::VE;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
     const int lane = threadIdx.x & 31;
+    int64_t row0, row1;
+    rows.resolve(row0, row1);
     const int64_t n_warps = (int64_t(gridDim.x) * kStreamThreads) >> 5;
-    const int64_t per_warp = (n_rows + n_warps - 1) / n_warps;
-    const int64_t r_begin = ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
-    const int64_t r_end = r_begin + per_warp < n_rows ? r_begin + per_warp : n_rows;
+    const int64_t per_warp = (row1 - row0 + n_warps - 1) / n_warps;
+    const int64_t r_begin = row0 + ((int64_t(blockIdx.x) * kStreamThreads + threadIdx.x) >> 5) * per_warp;
+    const int64_t r_end = r_begin + per_warp < row1 ? r_begin + per_warp : row1;
     if (r_begin >= r_end) return;
     bool ignored = false;
     RowWalker rw;
@@ -202,10 +212,15 @@ grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, int6
 template <typename T>
 static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int32_t *lx, const int32_t *ly,
                                  const int32_t *y, const Workspace &w, const void *grad_costs, int32_t gc_stride,
-                                 T *gx, cudaStream_t s)
+                                 T *gx, cudaStream_t s, const GradRows &span)
 {
     using CostT = typename Elt<T>::cost;
     if (p.n_rows == 0) return cudaSuccess;
+    // rows of this launch: everything, or a sequence group whose bounds only the device knows; the grid is then
+    // sized for span.grid_rows rows (the kernels cope with a longer range, more slowly)
+    const RowRange rows{0, p.n_rows, span.device_range};
+    const int64_t n_rows = span.device_range ? (span.grid_rows < p.n_rows ? span.grid_rows : p.n_rows) : p.n_rows;
+    if (n_rows <= 0) return cudaSuccess;
     constexpr int VE = Elt<T>::VE;
     const CostT *gc = static_cast<const CostT *>(grad_costs);
     const double mean_inv =
@@ -213,8 +228,8 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     const bool aligned = (p.V % VE == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
                          (reinterpret_cast<uintptr_t>(gx) % 16 == 0);
     if (!(p.flags & CWRNNT_FUSED_LOG_SOFTMAX)) {
-        const unsigned grid = tiled_grid(p.n_rows, 8 * 4);  // 8 warps, 4 rows each
-        grad_rows_sparse_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
+        const unsigned grid = tiled_grid(n_rows, 8 * 4);  // 8 warps, 4 rows each
+        grad_rows_sparse_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, rows, p.B, lx, ly, y, p.y_stride,
                                                                    p.blank, p.flags, mean_inv, w, gc, gc_stride,
                                                                    aligned ? 1 : 0);
         return cudaGetLastError();
@@ -229,9 +244,9 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
         const int run_len = row_bytes >= 8192 ? 8 : (row_bytes >= 4096 ? 1 : (row_bytes >= 2048 ? 2 : 8));
 #define LAUNCH(LPR, NV, FULL)                                                                                    \
     {                                                                                                            \
-        const unsigned grid = tiled_grid(p.n_rows, int64_t(kStreamThreads / LPR) * run_len);                     \
+        const unsigned grid = tiled_grid(n_rows, int64_t(kStreamThreads / LPR) * run_len);                       \
         grad_rows_kernel<T, LPR, NV, FULL><<<grid, kStreamThreads, 0, s>>>(                                      \
-            x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride,      \
+            x, gx, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride,          \
             run_len);                                                                                            \
     }
 #define CALL(LPR, NV)                    \
@@ -243,30 +258,79 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
 #undef CALL
 #undef LAUNCH
     } else {
-        const unsigned grid = tiled_grid(p.n_rows, 8 * 4);
-        grad_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, p.n_rows, p.B, lx, ly, y, p.y_stride,
+        const unsigned grid = tiled_grid(n_rows, 8 * 4);
+        grad_rows_generic_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, rows, p.B, lx, ly, y, p.y_stride,
                                                                     p.blank, p.flags, mean_inv, w, gc, gc_stride);
     }
     return cudaGetLastError();
 }
 
+// In-place scaling of a gradient that was computed for an upstream gradient of 1 (cwrnnt_loss_grad). The usual
+// upstream gradient of a training loss IS 1: every thread reads the factor first and leaves if there is nothing to do,
+// so that case costs one empty launch and no memory traffic.
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads)
+scale_kernel(T *__restrict__ g, int64_t n, const typename Elt<T>::cost *__restrict__ factor)
+{
+    using E = Elt<T>;
+    using A = typename E::acc;
+    constexpr int VE = E::VE;
+    const A f = A(__ldg(factor));
+    if (f == A(1)) return;
+    const int64_t stride = int64_t(gridDim.x) * kStreamThreads;
+    const int64_t tid = int64_t(blockIdx.x) * kStreamThreads + threadIdx.x;
+    const int64_t head = reinterpret_cast<uintptr_t>(g) % 16 ? n : 0;  // unaligned base: everything element-wise
+    const int64_t nvec = (n - head) / VE;
+    uint4 *gv = reinterpret_cast<uint4 *>(g + head);
+    for (int64_t i = tid; i < nvec; i += stride) {
+        A e[VE];
+        E::unpack(gv[i], e);
+#pragma unroll
+        for (int c = 0; c < VE; ++c) e[c] *= f;
+        gv[i] = E::pack(e);
+    }
+    for (int64_t i = (head ? 0 : nvec * VE) + tid; i < n; i += stride) g[i] = E::from_acc(E::to_acc(g[i]) * f);
+}
+
+template <typename T>
+static cudaError_t launch_scale_t(const cwrnnt_problem &p, T *g, const void *factor, cudaStream_t s)
+{
+    const int64_t n = p.n_rows * int64_t(p.V);
+    if (n == 0) return cudaSuccess;
+    const int64_t want = (n / Elt<T>::VE + kStreamThreads - 1) / kStreamThreads;
+    const int grid = int(want < 1 ? 1 : (want < kNumSMs * 16 ? want : kNumSMs * 16));
+    scale_kernel<T><<<grid, kStreamThreads, 0, s>>>(g, n, static_cast<const typename Elt<T>::cost *>(factor));
+    return cudaGetLastError();
+}
+
+cudaError_t launch_scale(const cwrnnt_problem &p, void *grad_x, const void *factor, cudaStream_t s)
+{
+    switch (p.dtype) {
+    case CWRNNT_F32: return launch_scale_t(p, static_cast<float *>(grad_x), factor, s);
+    case CWRNNT_F16: return launch_scale_t(p, static_cast<__half *>(grad_x), factor, s);
+    case CWRNNT_BF16: return launch_scale_t(p, static_cast<__nv_bfloat16 *>(grad_x), factor, s);
+    case CWRNNT_F64: return launch_scale_t(p, static_cast<double *>(grad_x), factor, s);
+    }
+    return cudaErrorInvalidValue;
+}
+
 cudaError_t launch_grad(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
                         const int32_t *y, const Workspace &w, const void *grad_costs, int32_t gc_stride, void *grad_x,
-                        cudaStream_t s)
+                        cudaStream_t s, const GradRows &span)
 {
     switch (p.dtype) {
     case CWRNNT_F32:
         return launch_grad_t(p, static_cast<const float *>(x), lx, ly, y, w, grad_costs, gc_stride,
-                             static_cast<float *>(grad_x), s);
+                             static_cast<float *>(grad_x), s, span);
     case CWRNNT_F16:
         return launch_grad_t(p, static_cast<const __half *>(x), lx, ly, y, w, grad_costs, gc_stride,
-                             static_cast<__half *>(grad_x), s);
+                             static_cast<__half *>(grad_x), s, span);
     case CWRNNT_BF16:
         return launch_grad_t(p, static_cast<const __nv_bfloat16 *>(x), lx, ly, y, w, grad_costs, gc_stride,
-                             static_cast<__nv_bfloat16 *>(grad_x), s);
+                             static_cast<__nv_bfloat16 *>(grad_x), s, span);
     case CWRNNT_F64:
         return launch_grad_t(p, static_cast<const double *>(x), lx, ly, y, w, grad_costs, gc_stride,
-                             static_cast<double *>(grad_x), s);
+                             static_cast<double *>(grad_x), s, span);
     }
     return cudaErrorInvalidValue;
 }

@@ -7,15 +7,16 @@ namespace cwrnnt {
 // Text returned by cwrnnt_last_error() on the calling thread.
 void set_last_error(const char *text);
 
-// K0: offsets, validation, longest-first order. 1 CTA.
+// K0: offsets, validation, longest-first order, first row of every sequence group of `plan`. 1 CTA.
 cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                        void *costs, cudaStream_t s);
+                        void *costs, cudaStream_t s, GroupPlan plan = GroupPlan{1, 1});
 
 cudaError_t launch_offsets_only(const int32_t *lx, const int32_t *ly, int B, int max_u, int64_t *off, cudaStream_t s);
 
-// K1: row log-sum-exp + blank/label log-prob gather into the diagonal-major arrays.
+// K1: row log-sum-exp + blank/label log-prob gather into the diagonal-major arrays, rows [row0, row1)
+// (row1 < 0: up to the last row).
 cudaError_t launch_gather(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
-                          const int32_t *y, const Workspace &w, cudaStream_t s);
+                          const int32_t *y, const Workspace &w, cudaStream_t s, int64_t row0 = 0, int64_t row1 = -1);
 
 // Sharded runs: where the costs go besides the local [B] array (see cwrnnt_forward_sharded).
 struct ShardOutput {
@@ -24,14 +25,24 @@ struct ShardOutput {
     void *cost_vector;          // [n_global + 1], costs type
 };
 
-// K2: alpha/beta anti-diagonal wavefront, costs, loss.
+// K2: alpha/beta anti-diagonal wavefront, costs, loss. With a plan of several groups, one launch per group: only the
+// sequences of `group` run, and the CTA that takes the last completion ticket over ALL launches writes costs and loss.
 cudaError_t launch_wavefront(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                             void *costs, void *loss, const ShardOutput *shard, cudaStream_t s);
+                             void *costs, void *loss, const ShardOutput *shard, cudaStream_t s,
+                             GroupPlan plan = GroupPlan{1, 1}, int group = 0);
 
-// K3: dense gradient in one streaming pass.
+// K3: dense gradient in one streaming pass, over all rows or over the rows device_range[0] .. device_range[1]
+// (a sequence group; the pair lives in device memory, the grid is sized for grid_rows rows).
+struct GradRows {
+    const int64_t *device_range;
+    int64_t grid_rows;
+};
 cudaError_t launch_grad(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
                         const int32_t *y, const Workspace &w, const void *grad_costs, int32_t gc_stride, void *grad_x,
-                        cudaStream_t s);
+                        cudaStream_t s, const GradRows &span = GradRows{nullptr, 0});
+
+// grad_x *= *factor (a device scalar of the costs' type); returns at once on the device when the factor is 1.
+cudaError_t launch_scale(const cwrnnt_problem &p, void *grad_x, const void *factor, cudaStream_t s);
 
 // Reference-shaped exports.
 cudaError_t launch_pair_grads(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,

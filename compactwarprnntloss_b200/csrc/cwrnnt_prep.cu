@@ -12,7 +12,7 @@ constexpr int kSortLimit = 4096;  // rank sort is O(B^2 / threads); beyond this 
 template <typename CostT>
 __global__ void __launch_bounds__(kPrepThreads)
 prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int B, int64_t n_rows, int max_u,
-            Workspace w, CostT *__restrict__ costs, int64_t *off_only)
+            Workspace w, CostT *__restrict__ costs, int64_t *off_only, GroupPlan plan)
 {
     __shared__ int64_t part[kPrepThreads];
     __shared__ int bad_first;
@@ -71,6 +71,17 @@ prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int 
         return;
     }
 
+    // first row of every sequence group (group = nominal row range that holds a sequence's last row; groups are
+    // runs of consecutive sequences, possibly empty): bounds[g] = off[first sequence whose group is >= g]
+    __syncthreads();  // off[] complete
+    for (int n = tid; n < B; n += kPrepThreads) {
+        const int g_here = group_of_row(off[n + 1] - 1, plan);
+        const int g_prev = n > 0 ? group_of_row(off[n] - 1, plan) : -1;
+        for (int g = g_prev + 1; g <= g_here; ++g) w.bounds[g] = off[n];
+    }
+    if (tid == 0)
+        for (int g = (B > 0 ? group_of_row(total - 1, plan) : -1) + 1; g <= kMaxGroups; ++g) w.bounds[g] = total;
+
     // longest wavefront first: key = T+U, ties by index (stable, deterministic)
     if (B <= kSortLimit) {
         for (int n = tid; n < B; n += kPrepThreads) keys[n] = lx[n] + ly[n];
@@ -87,14 +98,15 @@ prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int 
 }
 
 cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                        void *costs, cudaStream_t s)
+                        void *costs, cudaStream_t s, GroupPlan plan)
 {
+    if (plan.count < 1 || plan.count > kMaxGroups || plan.range_rows < 1) return cudaErrorInvalidValue;
     if (p.dtype == CWRNNT_F64)
         prep_kernel<double><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
-                                                       static_cast<double *>(costs), nullptr);
+                                                       static_cast<double *>(costs), nullptr, plan);
     else
         prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
-                                                      static_cast<float *>(costs), nullptr);
+                                                      static_cast<float *>(costs), nullptr, plan);
     return cudaGetLastError();
 }
 
@@ -102,7 +114,7 @@ cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_
 cudaError_t launch_offsets_only(const int32_t *lx, const int32_t *ly, int B, int max_u, int64_t *off, cudaStream_t s)
 {
     Workspace none{};
-    prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, B, 0, max_u, none, nullptr, off);
+    prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, B, 0, max_u, none, nullptr, off, GroupPlan{1, 1});
     return cudaGetLastError();
 }
 

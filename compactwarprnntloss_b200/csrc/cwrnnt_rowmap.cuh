@@ -6,6 +6,18 @@ namespace cwrnnt {
 
 constexpr int kStreamThreads = 256;  // 8 warps per CTA in the streaming kernels
 
+// Rows covered by one launch of a streaming kernel: [begin, end). A pipelined step knows the rows of a sequence group
+// only on the device (K0 computes them): then `dev` points at the pair and begin/end are ignored.
+struct RowRange {
+    int64_t begin, end;
+    const int64_t *dev;
+    __device__ __forceinline__ void resolve(int64_t &b, int64_t &e) const
+    {
+        b = dev ? __ldg(dev) : begin;
+        e = dev ? __ldg(dev + 1) : end;
+    }
+};
+
 // Position of one lattice row while a group of lanes walks a contiguous run of rows. Found once per run by bisection
 // and one division, then advanced with a handful of integer operations per row - rows are visited in memory order,
 // which is (sequence, t, u) order.

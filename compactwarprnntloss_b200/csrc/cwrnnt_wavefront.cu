@@ -289,7 +289,18 @@ struct WaveArgs {
     const int32_t *global_ids;
     int n_global;
     CostT *cost_vec;
+    // pipelined step: this launch runs the sequences of one group only; tickets are counted over all launches
+    GroupPlan plan;
+    int group;
+    unsigned int ticket_total;
 };
+
+// True when sequence n is left to another launch of a pipelined step.
+template <typename CostT>
+__device__ __forceinline__ bool other_group(const WaveArgs<CostT> &g, int n)
+{
+    return g.plan.count > 1 && group_of_row(g.w.off[n + 1] - 1, g.plan) != g.group;
+}
 
 // Completion ticket: the last CTA of the grid turns the per-sequence log-likelihoods into costs, status and loss.
 template <typename CostT>
@@ -301,7 +312,7 @@ __device__ __forceinline__ void finalize_if_last(const WaveArgs<CostT> &g, int n
     cta_sync(n_active);
     if (threadIdx.x == 0) {
         const unsigned int t = atomicAdd(w.ticket, 1u);
-        *last_flag = (t == gridDim.x - 1);
+        *last_flag = (t == g.ticket_total - 1);
     }
     cta_sync(n_active);
     if (!*last_flag) return;
@@ -359,6 +370,10 @@ wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
     const int n = w.order[blockIdx.x / g.n_dirs];
+    if (other_group(g, n)) {  // one warp stays to take this CTA's completion ticket
+        if (threadIdx.x < 32) finalize_if_last(g, 32, edge, &last_flag);
+        return;
+    }
     const bool beta_dir = (g.n_dirs == 1) || (blockIdx.x & 1);
     const int T = g.lx[n], U = g.ly[n];
     const int64_t off = w.off[n];
@@ -389,7 +404,9 @@ wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g
 // shuffles, no warp-seam special case). One named barrier per step joins all warps of the CTA.
 // Hand-over of ring slot x % R (operands of step x): the helper's copy group for step s+2 is complete before the
 // barrier that ends step s; the compute warp reads the operands of step s+1 during step s (one step ahead, into
-// registers); the helper refills slot s % R during step s, after its last read during step s-1.
+// registers); the helper refills slot s % R during step s, after its last read during step s-1. Step 0's operands
+// are read before the loop, between two start barriers, so that the refill of slot 0 during step 0 cannot overtake
+// that read.
 template <int R, bool F64, bool BETA>
 __device__ __forceinline__ void run_direction_split(int T, int U, const double *__restrict__ lpb,
                                                     const double *__restrict__ lpl, double *__restrict__ out,
@@ -439,7 +456,10 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
         cp_async_wait<R - 2>();  // operands of steps 0 and 1 are in place
         int tprev = u <= U ? (BETA ? nd - u : -u - 1) : INT_MIN / 2;  // frame index of this column one step ago
         int last_base = 0;
-        asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");      // start barrier
+        asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");      // start barrier: steps 0 and 1 are staged
+        // second barrier: the compute warps have taken the operands of step 0 out of slot 0, which the first
+        // iteration below refills
+        asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
 
         // step s: store the result of step s-1, refill slot s % R with the operands of step s+R
         for (int s0 = 0; s0 <= nd; s0 += R) {
@@ -477,6 +497,7 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
     const int nb_col = BETA ? (u >= U ? n_cols : u + 1) : (u == 0 ? n_cols : u - 1);
     asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");  // start barrier: operands of steps 0 and 1 are staged
     double cur_b = st_b[0], cur_l = st_l[0];
+    asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");  // slot 0 is read: the helper may refill it
     for (int s0 = 0; s0 < nd; s0 += R) {
 #pragma unroll
         for (int k = 0; k < R; ++k) {
@@ -511,6 +532,10 @@ wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::t
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
     const int n = w.order[blockIdx.x / g.n_dirs];
+    if (other_group(g, n)) {  // one warp stays to take this CTA's completion ticket
+        if (threadIdx.x < 32) finalize_if_last(g, 32, edge, &last_flag);
+        return;
+    }
     const bool beta_dir = (g.n_dirs == 1) || (blockIdx.x & 1);
     const int T = g.lx[n], U = g.ly[n];
     const int64_t off = w.off[n];
@@ -550,7 +575,8 @@ static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
 
 template <bool F64>
 static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                                      void *costs, void *loss, const ShardOutput *shard, cudaStream_t s)
+                                      void *costs, void *loss, const ShardOutput *shard, cudaStream_t s,
+                                      GroupPlan plan, int group)
 {
     using CostT = typename std::conditional<F64, double, float>::type;
     if (p.B == 0) return cudaSuccess;
@@ -571,6 +597,9 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
     }
     const int cols = p.max_u + 1;
     const int grid = p.B * g.n_dirs;
+    g.plan = plan;
+    g.group = group;
+    g.ticket_total = unsigned(grid) * unsigned(plan.count);
     cudaError_t e = cudaSuccess;
 
     if (cols <= 512) {
@@ -608,10 +637,11 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
 }
 
 cudaError_t launch_wavefront(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                             void *costs, void *loss, const ShardOutput *shard, cudaStream_t s)
+                             void *costs, void *loss, const ShardOutput *shard, cudaStream_t s, GroupPlan plan,
+                             int group)
 {
-    return p.dtype == CWRNNT_F64 ? launch_wavefront_t<true>(p, lx, ly, w, costs, loss, shard, s)
-                                 : launch_wavefront_t<false>(p, lx, ly, w, costs, loss, shard, s);
+    return p.dtype == CWRNNT_F64 ? launch_wavefront_t<true>(p, lx, ly, w, costs, loss, shard, s, plan, group)
+                                 : launch_wavefront_t<false>(p, lx, ly, w, costs, loss, shard, s, plan, group);
 }
 
 }  // namespace cwrnnt

@@ -8,8 +8,10 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <mutex>
 #include <string>
 #include <tuple>
+#include <vector>
 
 #include "cwarp_rnnt_b200.h"
 
@@ -129,6 +131,53 @@ torch::Tensor rnnt_backward(const torch::Tensor &xs, const torch::Tensor &lx, co
                                  gc.numel() == 1 ? 0 : 1, gx.data_ptr(), current_stream()),
                  "cwrnnt_backward");
     return gx;
+}
+
+// Side streams of the pipelined step, one set per device, created on first use and kept for the life of the process.
+cwrnnt_pipe *pipe_of(int device_index)
+{
+    static std::mutex lock;
+    static std::vector<cwrnnt_pipe *> pipes;
+    std::lock_guard<std::mutex> hold(lock);
+    if (device_index >= static_cast<int>(pipes.size())) pipes.resize(device_index + 1, nullptr);
+    if (!pipes[device_index]) check_status(cwrnnt_pipe_create(&pipes[device_index]), "cwrnnt_pipe_create");
+    return pipes[device_index];
+}
+
+// Forward and gradient in one pipelined call, for an upstream gradient of 1 (scaled later by rnnt_scale_grad if the
+// real one differs). Returns (costs [N], loss [], workspace bytes, grad_x like xs).
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor>
+rnnt_loss_grad(const torch::Tensor &xs, const torch::Tensor &lx, const torch::Tensor &ys, const torch::Tensor &ly,
+               int64_t blank, int64_t flags, int64_t mean_denominator, int64_t groups)
+{
+    check_inputs(xs, lx, ys, ly);
+    const c10::cuda::CUDAGuard guard(xs.device());
+    cwrnnt_problem p = describe(xs, lx, ys, blank, flags, mean_denominator);
+    auto ws = make_workspace(p, xs);
+    auto costs = torch::empty({lx.size(0)}, xs.options().dtype(cost_type(xs)));
+    auto loss = torch::zeros({}, costs.options());
+    auto gx = torch::empty_like(xs);
+    check_status(cwrnnt_loss_grad(pipe_of(xs.get_device()), &p, xs.data_ptr(), i32(lx), i32(ly), i32(ys),
+                                  ws.data_ptr(), ws.numel(), costs.data_ptr(), loss.data_ptr(), nullptr, 0,
+                                  gx.data_ptr(), nullptr, 0, nullptr, static_cast<int32_t>(groups), current_stream()),
+                 "cwrnnt_loss_grad");
+    return {costs, loss, ws, gx};
+}
+
+// grad_x *= factor in place; factor holds one element of the costs dtype on the same device.
+void rnnt_scale_grad(torch::Tensor grad_x, const torch::Tensor &factor)
+{
+    CHECK_CONTIGUOUS(grad_x);
+    CHECK_CUDA(grad_x);
+    CHECK_CUDA(factor);
+    TORCH_CHECK(grad_x.dim() == 2 && factor.numel() == 1, "grad_x must be 2-D and factor a single element");
+    const c10::cuda::CUDAGuard guard(grad_x.device());
+    cwrnnt_problem p{};
+    p.n_rows = grad_x.size(0);
+    p.V = static_cast<int32_t>(grad_x.size(1));
+    p.dtype = dtype_code(grad_x);
+    auto f = factor.to(cost_type(grad_x)).contiguous();
+    check_status(cwrnnt_scale_grad(&p, grad_x.data_ptr(), f.data_ptr(), current_stream()), "cwrnnt_scale_grad");
 }
 
 // Device status words of a workspace: synchronises the current stream. [bits, first bad sequence, rows, 0].
@@ -282,6 +331,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("_cwarp_rnnt_loss", &compact_rnnt_loss, "Transducer costs without gradients.");
     m.def("_rnnt_forward", &rnnt_forward, "Fused forward: (costs, loss, workspace).");
     m.def("_rnnt_backward", &rnnt_backward, "Fused backward: gradient w.r.t. xs.");
+    m.def("_rnnt_loss_grad", &rnnt_loss_grad,
+          "Pipelined forward + gradient for an upstream gradient of 1: (costs, loss, workspace, grad_x).");
+    m.def("_rnnt_scale_grad", &rnnt_scale_grad, "In-place grad_x *= factor (device scalar); free when the factor is 1.");
     m.def("_rnnt_status", &rnnt_status, "Status words of a workspace (synchronises).");
     m.def("_pack_padded", &pack_padded, "Padded [N,T,U+1,V] -> compact [n_rows,V].");
     m.def("_unpack_padded", &unpack_padded, "Compact [n_rows,V] -> zero-padded [N,T,U+1,V].");

@@ -9,6 +9,14 @@ fused_log_softmax   False (default, the reference contract): ``x`` holds log-pro
                     except at the blank and label columns. True: ``x`` holds raw logits; the row-wise log-softmax and
                     its backward are fused into the loss kernels and the gradient is dense. On already-normalised
                     input both settings return the same loss.
+eager_grad          True (default): when ``x`` requires a gradient and the reduction is 'mean' or 'sum', the gradient
+                    is computed inside the forward call, as the reference does (its forward returns the gradients,
+                    cwarp_rnnt/__init__.py:14-16), by the pipelined single-call step: the alpha/beta wavefront of each
+                    group of sequences runs on a side stream underneath the two bandwidth-bound passes. ``backward``
+                    then only scales the stored gradient (a no-op on the device when the upstream gradient is 1).
+                    False: the gradient pass runs inside ``backward`` with the upstream gradient folded in - one pass
+                    less when that gradient is not 1 (loss scaling), no overlap, and nothing computed if ``backward``
+                    is never called.
 check               True (default): the reference's assertions, including the one that reads ``ly.max()`` on the host,
                     plus a read of the device status word after the forward (one synchronisation). False: no host
                     synchronisation at all; invalid lengths then surface as NaN costs.
@@ -32,10 +40,14 @@ class _TransLoss(torch.autograd.Function):
     """forward -> (costs [N], loss []); only one of the two is consumed, depending on the reduction."""
 
     @staticmethod
-    def forward(ctx: Any, xs, lx, ys, ly, blank, flags, mean_denominator, check):
+    def forward(ctx: Any, xs, lx, ys, ly, blank, flags, mean_denominator, check, eager_grad):
         needs_grad = xs.requires_grad
-        run_flags = flags if needs_grad else (flags | core.COSTS_ONLY)
-        costs, loss, ws = core._rnnt_forward(xs, lx, ys, ly, blank, run_flags, mean_denominator)
+        ctx.grad_x = None
+        if needs_grad and eager_grad and flags & (core.REDUCE_MEAN | core.REDUCE_SUM):
+            costs, loss, ws, ctx.grad_x = core._rnnt_loss_grad(xs, lx, ys, ly, blank, flags, mean_denominator, 0)
+        else:
+            run_flags = flags if needs_grad else (flags | core.COSTS_ONLY)
+            costs, loss, ws = core._rnnt_forward(xs, lx, ys, ly, blank, run_flags, mean_denominator)
         if check:
             st = core._rnnt_status(ws)
             if st[0] & core.ST_BAD_LENGTH:
@@ -55,9 +67,15 @@ class _TransLoss(torch.autograd.Function):
         xs, lx, ys, ly, ws = ctx.saved_tensors
         reduced = ctx.flags & (core.REDUCE_MEAN | core.REDUCE_SUM)
         g = grad_loss if reduced else grad_costs
-        grad_x = core._rnnt_backward(xs, lx, ys, ly, ctx.blank, ctx.flags, ctx.mean_denominator, ws,
-                                     g.contiguous())
-        return grad_x, None, None, None, None, None, None, None
+        if ctx.grad_x is not None:
+            # computed during forward for an upstream gradient of 1; handed over once (a second backward over a
+            # retained graph recomputes it below from the saved workspace)
+            grad_x, ctx.grad_x = ctx.grad_x, None
+            core._rnnt_scale_grad(grad_x, g)
+        else:
+            grad_x = core._rnnt_backward(xs, lx, ys, ly, ctx.blank, ctx.flags, ctx.mean_denominator, ws,
+                                         g.contiguous())
+        return grad_x, None, None, None, None, None, None, None, None
 
 
 class _PackPadded(torch.autograd.Function):
@@ -84,7 +102,7 @@ def compact_from_padded(x: torch.Tensor, lx: torch.Tensor, ly: torch.Tensor) -> 
 def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torch.Tensor, blank: int = 0,
                     reduction: Optional[Literal["mean", "sum", "none"]] = "mean", *, gather: bool = True,
                     average_frames: bool = False, fused_log_softmax: bool = False, check: bool = True,
-                    mean_denominator: int = 0) -> torch.Tensor:
+                    mean_denominator: int = 0, eager_grad: bool = True) -> torch.Tensor:
     """Transducer loss with compact layout. See the module docstring for the keyword-only options."""
     del gather  # always on
     assert lx.dtype == torch.int32
@@ -122,7 +140,8 @@ def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torc
     elif not (reduction == "none" or reduction is None):
         raise ValueError
 
-    costs, loss = _TransLoss.apply(x.contiguous(), lx, y.contiguous(), ly, blank, flags, mean_denominator, check)
+    costs, loss = _TransLoss.apply(x.contiguous(), lx, y.contiguous(), ly, blank, flags, mean_denominator, check,
+                                   eager_grad)
     return loss if reduction in ("mean", "sum") else costs
 
 
@@ -130,11 +149,13 @@ class TransducerLoss(torch.nn.Module):
     """Module form of :func:`transducer_loss`."""
 
     def __init__(self, blank: int = 0, reduction: Optional[str] = "mean", average_frames: bool = False,
-                 fused_log_softmax: bool = False, check: bool = True):
+                 fused_log_softmax: bool = False, check: bool = True, eager_grad: bool = True):
         super().__init__()
         self.blank, self.reduction = blank, reduction
         self.average_frames, self.fused_log_softmax, self.check = average_frames, fused_log_softmax, check
+        self.eager_grad = eager_grad
 
     def forward(self, x, lx, y, ly):
         return transducer_loss(x, lx, y, ly, self.blank, self.reduction, average_frames=self.average_frames,
-                               fused_log_softmax=self.fused_log_softmax, check=self.check)
+                               fused_log_softmax=self.fused_log_softmax, check=self.check,
+                               eager_grad=self.eager_grad)

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CWRNNT_ABI_VERSION 1
+#define CWRNNT_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define CWRNNT_API __attribute__((visibility("default")))
@@ -139,6 +139,46 @@ CWRNNT_API int cwrnnt_forward_sharded(const cwrnnt_problem *p, const void *x, co
 CWRNNT_API int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
                     const void *workspace, const void *grad_costs, int32_t grad_costs_stride, void *grad_x,
                     cwrnnt_stream_t stream);
+
+/*
+ * One training step in one call: costs, loss AND the gradient, as a software pipeline over groups of sequences.
+ * Replaces what the reference's autograd forward already does in one go - _cwarp_rnnt_forward computes the gradients
+ * during the forward call and backward only scales them (cwarp_rnnt/__init__.py:10-29, cwarp_cuda.cpp:84-136) - and,
+ * with CWRNNT_FUSED_LOG_SOFTMAX, the caller's log_softmax forward and backward.
+ * The rows are cut into `groups` ranges; group g = the sequences whose last row lies in range g. On the caller's
+ * stream: K0, gather of range 0..G-1, then the gradient of group 0..G-1. On the pipe's high-priority side streams:
+ * the alpha/beta wavefront of group g as soon as range g is gathered. The wavefront (a chain of T+U dependent steps on
+ * a few SMs) thereby runs underneath the two bandwidth-bound passes instead of between them. Everything is joined
+ * back into `stream` before the call returns (event waits, nothing blocks the host), so results are ordered on
+ * `stream` exactly like those of cwrnnt_forward + cwrnnt_backward; they are bit-identical to that pair's.
+ *   pipe        side streams and events, from cwrnnt_pipe_create on the same device; one call at a time per pipe.
+ *               NULL runs the same work on `stream` alone without overlap.
+ *   grad_costs / grad_costs_stride / grad_x   as cwrnnt_backward (NULL grad_costs: upstream gradient 1)
+ *   global_ids / n_global / cost_vector       as cwrnnt_forward_sharded, or NULL / 0 / NULL
+ *   groups      0 = chosen from the size of x; 1..8 to force
+ * CWRNNT_COSTS_ONLY is refused (use cwrnnt_forward). The workspace ends up in the same state as after
+ * cwrnnt_forward, so cwrnnt_backward / cwrnnt_pair_grads / cwrnnt_export_alpha_beta may follow.
+ */
+typedef struct cwrnnt_pipe cwrnnt_pipe;
+CWRNNT_API int cwrnnt_pipe_create(cwrnnt_pipe **pipe);
+CWRNNT_API void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe);
+CWRNNT_API int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, const int32_t *lx,
+                                const int32_t *ly, const int32_t *y, void *workspace, int64_t workspace_bytes,
+                                void *costs, void *loss, const void *grad_costs, int32_t grad_costs_stride,
+                                void *grad_x, const int32_t *global_ids, int32_t n_global, void *cost_vector,
+                                int32_t groups, cwrnnt_stream_t stream);
+
+/* Number of sequence groups cwrnnt_loss_grad uses for this problem and `groups` argument (with a pipe); < 0 on bad
+ * arguments. A step then launches 1 + 3 * groups kernels. No counterpart in the reference. */
+CWRNNT_API int32_t cwrnnt_pipeline_groups(const cwrnnt_problem *p, int32_t groups);
+
+/*
+ * grad_x *= *factor in place; `factor` is one device scalar of the costs type. For a gradient that cwrnnt_loss_grad
+ * computed for an upstream gradient of 1 before the real one was known (autograd's backward arrives later): replaces
+ * the scaling step of the reference's backward (cwarp_cuda_rnnt_kernel.cu:512-521). When the factor is 1 - the usual
+ * case for a training loss - the kernel returns before touching grad_x.
+ */
+CWRNNT_API int cwrnnt_scale_grad(const cwrnnt_problem *p, void *grad_x, const void *factor, cwrnnt_stream_t stream);
 
 /*
  * The reference's intermediate results in the reference's own shapes, for callers of its extension module

@@ -130,6 +130,29 @@ def test_many_sequences_order_and_cursor(oracle):
     _check_fused(oracle, case, reduce="sum")
 
 
+def test_thousands_of_tiny_lattices_repeatedly(oracle):
+    """One- to sixteen-cell lattices, thousands of short-lived wavefront CTAs per launch: the schedule in which a helper
+    warp can get ahead of its compute warp. The first operands of a direction must be taken out of the staging ring
+    before the helper's first refill (a race here showed as a wrong beta(0,0) in a few of 4500 sequences per launch)."""
+    from compactwarprnntloss_b200 import capi
+    B = 4500
+    case = ragged_case(32, B, (1, 4), (0, 3), V=4)
+    want, _ = oracle.fused(case["x"], case["lx"], case["ly"], case["y"], 0, want_grad=False)
+    dev = torch.device("cuda:0")
+    x = torch.as_tensor(case["x"]).to(dev)
+    lx, ly = torch.as_tensor(case["lx"]).to(dev), torch.as_tensor(case["ly"]).to(dev)
+    y = torch.as_tensor(case["y"]).to(dev).contiguous()
+    p = capi.make_problem(x, lx, y, 0, capi.FUSED_LOG_SOFTMAX)
+    for rep in range(10):
+        ws = capi.alloc_workspace(p, dev)
+        if rep % 2:
+            ws.fill_(0xFF)  # NaN patterns wherever nothing is written
+        costs = torch.empty(B, device=dev)
+        capi.forward(p, x, lx, ly, y, ws, costs, None)
+        assert capi.read_status(ws)[0] == 0, rep
+        np.testing.assert_allclose(costs.cpu().numpy(), want, rtol=LOSS_RTOL, atol=1e-6, err_msg=f"launch {rep}")
+
+
 def test_costs_only_matches_full(oracle):
     from tests.gpu_helpers import run_engine
     case = ragged_case(12, 7, (2, 40), (0, 25), V=48)
