@@ -35,7 +35,7 @@ GroupPlan plan_groups(const cwrnnt_problem &p, int groups)
     // wavefronts are the critical path (4 x [1250 x 300] x 512: 1.48 ms against 1.85, 1.64 with 4)
     const int large = p.B <= 8 ? 8 : 4;
     const int want = groups > 0 ? groups : (bytes >= (int64_t(256) << 20) ? large : (bytes >= (int64_t(32) << 20) ? 2 : 1));
-    const int64_t kAlign = 2048;  // whole tiles of every row shape of the streaming kernels
+    const int64_t kAlign = 512;  // whole tiles of every row shape of the streaming kernels (at most 64 runs of 8 rows)
     GroupPlan plan{1, p.n_rows > 0 ? p.n_rows : 1};
     if (want > 1 && p.n_rows > kAlign) {
         plan.range_rows = align_up((p.n_rows + want - 1) / want, kAlign);
