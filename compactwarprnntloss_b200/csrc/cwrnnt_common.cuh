@@ -152,6 +152,12 @@ struct Elt<float> {
     }
     static __device__ __forceinline__ float to_acc(float v) { return v; }
     static __device__ __forceinline__ float from_acc(float v) { return v; }
+    // largest element of a vector (NaNs are skipped, as by a chain of `>` comparisons)
+    static __device__ __forceinline__ float vec_max(const uint4 &v)
+    {
+        return fmaxf(fmaxf(__uint_as_float(v.x), __uint_as_float(v.y)),
+                     fmaxf(__uint_as_float(v.z), __uint_as_float(v.w)));
+    }
 };
 
 template <>
@@ -182,6 +188,14 @@ struct Elt<__half> {
     }
     static __device__ __forceinline__ float to_acc(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half from_acc(float v) { return __float2half_rn(v); }
+    // the maximum is exact in any precision: three packed half2 maxima, then one widening
+    static __device__ __forceinline__ float vec_max(const uint4 &v)
+    {
+        const __half2 a = *reinterpret_cast<const __half2 *>(&v.x), b = *reinterpret_cast<const __half2 *>(&v.y);
+        const __half2 c = *reinterpret_cast<const __half2 *>(&v.z), d = *reinterpret_cast<const __half2 *>(&v.w);
+        const float2 m = __half22float2(__hmax2(__hmax2(a, b), __hmax2(c, d)));
+        return fmaxf(m.x, m.y);
+    }
 };
 
 template <>
@@ -211,6 +225,16 @@ struct Elt<__nv_bfloat16> {
     }
     static __device__ __forceinline__ float to_acc(__nv_bfloat16 v) { return __bfloat162float(v); }
     static __device__ __forceinline__ __nv_bfloat16 from_acc(float v) { return __float2bfloat16_rn(v); }
+    static __device__ __forceinline__ float vec_max(const uint4 &v)
+    {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&v.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&v.y);
+        const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162 *>(&v.z);
+        const __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162 *>(&v.w);
+        const __nv_bfloat162 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+        const unsigned int w = *reinterpret_cast<const unsigned int *>(&m);
+        return fmaxf(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
 };
 
 template <>
@@ -230,6 +254,10 @@ struct Elt<double> {
     }
     static __device__ __forceinline__ double to_acc(double v) { return v; }
     static __device__ __forceinline__ double from_acc(double v) { return v; }
+    static __device__ __forceinline__ double vec_max(const uint4 &v)
+    {
+        return fmax(__hiloint2double(int(v.y), int(v.x)), __hiloint2double(int(v.w), int(v.z)));
+    }
 };
 
 __device__ __forceinline__ float ex2_approx(float x)

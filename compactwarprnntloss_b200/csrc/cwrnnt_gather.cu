@@ -63,10 +63,8 @@ gather_rows_kernel(const T *__restrict__ x, int V, RowRange rows, int B, const i
 #pragma unroll
             for (int j = 0; j < NV; ++j) {
                 if (live && (FULL || j * LPR + gl < nvec)) {
-                    A e[VE];
-                    E::unpack(v[j], e);
-#pragma unroll
-                    for (int c = 0; c < VE; ++c) mx = e[c] > mx ? e[c] : mx;
+                    const A m = E::vec_max(v[j]);
+                    mx = m > mx ? m : mx;
                 }
             }
             mx = group_max<LPR>(mx);
@@ -92,6 +90,85 @@ gather_rows_kernel(const T *__restrict__ x, int V, RowRange rows, int B, const i
                 }
                 rw.advance(w.off, B, lx, ly);
             }
+        }
+    }
+    if (any_bad) atomicOr(w.status, CWRNNT_ST_BAD_LABEL);
+}
+
+// Rows beyond the register-resident shapes (more than 512 vectors: V > 2048 floats, > 4096 halves): one warp per row,
+// the row passing through the registers in segments of 32 lanes x 8 vectors (4 KB). Every segment gets its own shifted
+// sum and its own log-sum-exp in double; segments combine as log(exp(a) + exp(b)) in double. Any vector-aligned V,
+// however long. (For 8 KB rows the one-piece shape {32,16} is faster: 1.46 against 1.98 ms on 5.1 GB of bfloat16 -
+// the segments' reductions run one after the other - so this kernel starts where that shape ends.)
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads)
+gather_rows_long_kernel(const T *__restrict__ x, int V, RowRange rows, int B, const int32_t *__restrict__ lx,
+                        const int32_t *__restrict__ ly, const int32_t *__restrict__ y, int y_stride, int blank,
+                        Workspace w, int run_len)
+{
+    using E = Elt<T>;
+    using A = typename E::acc;
+    constexpr int VE = E::VE;
+    constexpr int NV = 8;
+    constexpr int kWarps = kStreamThreads / 32;
+    if (w.status[0] & CWRNNT_ST_FATAL) return;
+
+    const int lane = threadIdx.x & 31;
+    const int nvec = V / VE;
+    int64_t r_begin, r_end;
+    rows.resolve(r_begin, r_end);
+    const int64_t tile_rows = int64_t(kWarps) * run_len;
+    bool any_bad = false;
+
+    RowWalker rw;
+    for (int64_t tile = r_begin + blockIdx.x * tile_rows; tile < r_end; tile += gridDim.x * tile_rows) {
+        const int64_t first = tile + (threadIdx.x >> 5) * run_len;
+        const int64_t limit = first + run_len < r_end ? first + run_len : r_end;
+        for (int64_t r = first; r < limit; ++r) {  // a warp owns its rows: no shuffle crosses a row boundary
+            if (r == first) rw.start(r, w.off, B, lx, ly);
+            const T *row = x + r * int64_t(V);
+            const uint4 *rv = reinterpret_cast<const uint4 *>(row);
+            const int label = rw.label(y, y_stride, V, any_bad);
+            const A xb = E::to_acc(__ldg(row + blank));
+            const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
+            double lse = -INFINITY;
+            for (int seg = 0; seg < nvec; seg += 32 * NV) {
+                uint4 v[NV];
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    if (seg + j * 32 + lane < nvec) v[j] = ld_nc(rv + seg + j * 32 + lane);
+                A mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    if (seg + j * 32 + lane < nvec) {
+                        const A m = E::vec_max(v[j]);
+                        mx = m > mx ? m : mx;
+                    }
+                }
+                mx = group_max<32>(mx);
+                const RowShift<A> shift(mx);
+                A sum = A(0);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    if (seg + j * 32 + lane < nvec) {
+                        A e[VE];
+                        E::unpack(v[j], e);
+#pragma unroll
+                        for (int c = 0; c < VE; ++c) sum += shift.term(e[c]);
+                    }
+                }
+                sum = group_sum<32>(sum);
+                const double seg_lse = shift.lse(sum);  // every segment holds at least one element: sum >= 1
+                const double hi = fmax(lse, seg_lse), lo = fmin(lse, seg_lse);
+                lse = lo == -INFINITY ? hi : hi + log1p(exp(lo - hi));
+            }
+            if (lane == 0) {
+                const int64_t at = rw.off + rw.at;
+                w.lse[r] = lse;
+                w.lp_blank[at] = double(xb) - lse;
+                if (label >= 0) w.lp_label[at] = double(xl) - lse;
+            }
+            rw.advance(w.off, B, lx, ly);
         }
     }
     if (any_bad) atomicOr(w.status, CWRNNT_ST_BAD_LABEL);
@@ -185,9 +262,15 @@ static cudaError_t launch_gather_t(const cwrnnt_problem &p, const T *x, const in
         return cudaGetLastError();
     }
     RowShape shape{};
-    const bool vec_ok = (p.V % VE == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
-                        pick_row_shape(p.V / VE, &shape);
-    if (vec_ok) {
+    const bool aligned = (p.V % VE == 0) && (reinterpret_cast<uintptr_t>(x) % 16 == 0);
+    const bool vec_ok = aligned && pick_row_shape(p.V / VE, &shape);
+    if (aligned && !vec_ok) {
+        // long rows, in 4 KB segments; 8 rows per warp keep a CTA's tile at 64 rows
+        const int run_len = 8;
+        const unsigned grid = tiled_grid(n_rows, int64_t(kStreamThreads / 32) * run_len);
+        gather_rows_long_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank,
+                                                                   w, run_len);
+    } else if (vec_ok) {
         const bool full = (p.V / VE) == shape.lpr * shape.nv;
         // rows per lane group: long enough to amortise locating the run's first row (bisection, one division),
         // short enough that the CTAs in flight stay one compact front in memory (measured 1..32: 8 is best from

@@ -89,7 +89,8 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange ro
             const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
             const double lse = __ldg(w.lse + r);
             double wb, wl;
-            row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb, wl);
+            row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb,
+                             wl);
             const A tot = A(wb + wl);
             const A lse_a = A(lse);
 #pragma unroll
@@ -109,6 +110,78 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange ro
                 orow[blank] = E::from_acc(gb);
             }
             if (label >= 0 && label != blank && (label / VE) % LPR == gl)
+                orow[label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
+            rw.advance(w.off, B, lx, ly);
+        }
+    }
+}
+
+// Rows beyond the register-resident shapes (more than 512 vectors): one warp per row, the row in segments of 32 lanes
+// x 8 vectors. The gradient is element-wise once the row's scalars are known, so nothing is carried between segments.
+template <typename T>
+__global__ void __launch_bounds__(kStreamThreads)
+grad_rows_long_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange rows, int B,
+                      const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, const int32_t *__restrict__ y,
+                      int y_stride, int blank, int flags, double mean_inv, Workspace w,
+                      const typename Elt<T>::cost *__restrict__ grad_costs, int gc_stride, int run_len)
+{
+    using E = Elt<T>;
+    using A = typename E::acc;
+    using CostT = typename E::cost;
+    constexpr int VE = E::VE;
+    constexpr int NV = 8;
+    constexpr int kWarps = kStreamThreads / 32;
+    if (w.status[0] & CWRNNT_ST_FATAL) return;
+
+    const int lane = threadIdx.x & 31;
+    const int nvec = V / VE;
+    int64_t r_begin, r_end;
+    rows.resolve(r_begin, r_end);
+    const int64_t tile_rows = int64_t(kWarps) * run_len;
+    bool ignored = false;
+
+    RowWalker rw;
+    for (int64_t tile = r_begin + blockIdx.x * tile_rows; tile < r_end; tile += gridDim.x * tile_rows) {
+        const int64_t first = tile + (threadIdx.x >> 5) * run_len;
+        const int64_t limit = first + run_len < r_end ? first + run_len : r_end;
+        for (int64_t r = first; r < limit; ++r) {
+            if (r == first) rw.start(r, w.off, B, lx, ly);
+            const T *row = x + r * int64_t(V);
+            T *orow = gx + r * int64_t(V);
+            const uint4 *rv = reinterpret_cast<const uint4 *>(row);
+            uint4 *ov = reinterpret_cast<uint4 *>(orow);
+            const int label = rw.label(y, y_stride, V, ignored);
+            const A xb = E::to_acc(__ldg(row + blank));
+            const A xl = label >= 0 ? E::to_acc(__ldg(row + label)) : A(0);
+            const double lse = __ldg(w.lse + r);
+            double wb, wl;
+            row_terms<CostT>(rw, w, double(xb) - lse, double(xl) - lse, grad_costs, gc_stride, flags, mean_inv, wb,
+                             wl);
+            const A tot = A(wb + wl);
+            const A lse_a = A(lse);
+            for (int seg = 0; seg < nvec; seg += 32 * NV) {
+                uint4 v[NV];
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    if (seg + j * 32 + lane < nvec) v[j] = ld_nc(rv + seg + j * 32 + lane);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    if (seg + j * 32 + lane < nvec) {
+                        A e[VE];
+                        E::unpack(v[j], e);
+#pragma unroll
+                        for (int c = 0; c < VE; ++c) e[c] = exp_shifted(e[c], lse_a) * tot;
+                        ov[seg + j * 32 + lane] = E::pack(e);
+                    }
+                }
+            }
+            // the two sparse corrections, by the lane that stored the enclosing vector (same-thread program order)
+            if ((blank / VE) % 32 == lane) {
+                A gb = exp_shifted(xb, lse_a) * tot - A(wb);
+                if (label == blank) gb -= A(wl);
+                orow[blank] = E::from_acc(gb);
+            }
+            if (label >= 0 && label != blank && (label / VE) % 32 == lane)
                 orow[label] = E::from_acc(exp_shifted(xl, lse_a) * tot - A(wl));
             rw.advance(w.off, B, lx, ly);
         }
@@ -235,7 +308,12 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
         return cudaGetLastError();
     }
     RowShape shape{};
-    if (aligned && pick_row_shape(p.V / VE, &shape)) {
+    if (aligned && !pick_row_shape(p.V / VE, &shape)) {
+        const int run_len = 4;  // long rows, in 4 KB segments: 32 rows per CTA
+        const unsigned grid = tiled_grid(n_rows, int64_t(kStreamThreads / 32) * run_len);
+        grad_rows_long_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank,
+                                                                 p.flags, mean_inv, w, gc, gc_stride, run_len);
+    } else if (aligned && pick_row_shape(p.V / VE, &shape)) {
         const bool full = (p.V / VE) == shape.lpr * shape.nv;
         // rows per lane group, measured 1..32 on B200: a tile of 8 rows x 4 KB (run 1) or 16 rows x 2 KB (run 2)
         // per CTA streams best for the mixed read/write pattern; short rows are bound by per-row instructions and

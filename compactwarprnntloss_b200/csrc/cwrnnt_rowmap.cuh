@@ -93,7 +93,8 @@ struct RowWalker {
 };
 
 // Shape of the register-resident row: LPR lanes cooperate on one row, each holding NV 16-byte vectors.
-// Chosen from the number of vectors in a row; returns false when the row does not fit (generic path).
+// Chosen from the number of vectors in a row; returns false when the row does not fit (more than 512 vectors: the
+// segment-wise long-row kernels take over).
 struct RowShape {
     int lpr, nv;
 };

@@ -26,7 +26,10 @@
 // The last CTA to finish turns the per-sequence log-likelihoods into costs, the status bits and the reduced loss.
 #include <climits>
 #include <cstdio>
+#include <map>
+#include <mutex>
 #include <type_traits>
+#include <utility>
 
 #include "cwrnnt_kernels.h"
 
@@ -562,15 +565,32 @@ wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::t
     finalize_if_last(g, n_cols, edge, &last_flag);
 }
 
-template <typename K>
-static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
+// Dynamic shared memory above the default cap needs a per-kernel opt-in. It is asked for once per (device, kernel)
+// and size, so that repeated launches - and launches under stream capture after a first plain call - make no
+// attribute call at all.
+static cudaError_t opt_in_smem_impl(const void *kernel, size_t smem, int threads)
 {
     if (smem <= 32 * 1024) return cudaSuccess;  // default cap is 48 KB including ~9 KB of static arrays
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess)
+    static std::mutex lock;
+    static std::map<std::pair<int, const void *>, size_t> granted;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> hold(lock);
+    size_t &have = granted[std::make_pair(device, kernel)];
+    if (have >= smem) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e == cudaSuccess)
+        have = smem;
+    else
         std::fprintf(stderr, "cwrnnt: cannot opt in to %zu bytes of shared memory (%d threads): %s\n", smem, threads,
                      cudaGetErrorString(e));
     return e;
+}
+template <typename K>
+static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
+{
+    return opt_in_smem_impl(reinterpret_cast<const void *>(kernel), smem, threads);
 }
 
 template <bool F64>

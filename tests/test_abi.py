@@ -49,3 +49,36 @@ def test_null_pointers_are_rejected_before_any_launch():
     p = capi.Problem(n_rows=10, V=8, B=1, y_stride=1, max_u=1, blank=0, dtype=0, flags=0)
     assert L.cwrnnt_forward(ctypes.byref(p), None, None, None, None, None, 0, None, None, None) == 1
     assert L.cwrnnt_backward(ctypes.byref(p), None, None, None, None, None, None, 0, None, None) == 1
+
+
+def test_pipeline_group_plan_is_host_arithmetic():
+    """cwrnnt_pipeline_groups: the number of sequence groups of a pipelined step, from the problem's size alone."""
+    def groups(n_rows, V, B, dtype=capi.F32, forced=0):
+        p = capi.Problem(n_rows=n_rows, V=V, B=B, y_stride=80, max_u=80, blank=0, dtype=dtype,
+                         flags=capi.FUSED_LOG_SOFTMAX)
+        return capi.pipeline_groups(p, forced)
+
+    assert groups(314340, 1024, 32) == 4             # 1.29 GB, ordinary batch
+    assert groups(1420000, 512, 4) == 8              # a handful of long sequences
+    assert groups(40000, 256, 40) == 2               # 41 MB
+    assert groups(1500, 64, 4) == 1                  # small: no grouping
+    assert groups(314340, 1024, 32, forced=3) == 3
+    assert groups(300, 1024, 32, forced=8) == 1      # fewer rows than one aligned range
+    assert groups(3000, 64, 4, forced=8) == 6        # ranges are multiples of 512 rows
+    assert groups(3600000, 128, 256, dtype=capi.F16) == 4
+    L = capi.lib()
+    p = capi.Problem(n_rows=10, V=8, B=1, y_stride=1, max_u=1, blank=0, dtype=0, flags=0)
+    assert L.cwrnnt_pipeline_groups(ctypes.byref(p), 9) < 0
+    assert L.cwrnnt_pipeline_groups(ctypes.byref(p), -1) < 0
+
+
+def test_pipelined_step_rejects_bad_arguments_before_any_launch():
+    L = capi.lib()
+    p = capi.Problem(n_rows=10, V=8, B=1, y_stride=1, max_u=1, blank=0, dtype=0, flags=capi.COSTS_ONLY)
+    args = [None] * 5 + [0, None, None, None, 0, None, None, 0, None, 0, None]
+    assert L.cwrnnt_loss_grad(None, ctypes.byref(p), *args) == 1       # costs-only has no gradient
+    p.flags = 0
+    assert L.cwrnnt_loss_grad(None, ctypes.byref(p), *args) == 1       # null pointers
+    args[-2] = 9
+    assert L.cwrnnt_loss_grad(None, ctypes.byref(p), *args) == 1       # more groups than supported
+    assert L.cwrnnt_scale_grad(ctypes.byref(p), None, None, None) == 1

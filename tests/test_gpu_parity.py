@@ -57,14 +57,14 @@ def _check_fused(oracle, case, dtype=torch.float32, **kw):
     return got, costs, dense
 
 
-@pytest.mark.parametrize("V", [3, 5, 8, 32, 64, 100, 128, 257, 512, 1024, 2048, 4100])
+@pytest.mark.parametrize("V", [3, 5, 8, 32, 64, 100, 128, 257, 512, 1024, 2048, 4100, 8192])
 def test_fused_float32_vocab_sizes(oracle, V):
     case = ragged_case(V, 5, (1, 23), (0, 9), V=V, sigma=2.0)
     _check_fused(oracle, case, grad_costs=np.linspace(0.5, 1.5, 5))
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float64])
-@pytest.mark.parametrize("V", [6, 64, 128, 1024, 4096])
+@pytest.mark.parametrize("V", [6, 64, 128, 1024, 4096, 8200])
 def test_fused_other_dtypes(oracle, dtype, V):
     case = ragged_case(1000 + V, 4, (2, 17), (0, 8), V=V, sigma=1.5)
     _check_fused(oracle, case, dtype=dtype)

@@ -220,3 +220,38 @@ def test_autograd_eager_gradient_equals_deferred(oracle, fused):
             torch.testing.assert_close(g1, g0, rtol=2e-6, atol=1e-8)
     run(True, 1.0, twice=True)
     run(True, 3.0, twice=True)
+
+
+def test_pipelined_step_captured_in_a_cuda_graph(pipe, oracle):
+    """Fork and join are event waits, so the whole pipelined step - side streams included - is captured into one CUDA
+    graph. Group membership is worked out on the device, so the graph can be replayed on other lengths as long as the
+    row and sequence counts stay: here the same sequences in another order, with new logits."""
+    case = ragged_case(41, 12, (10, 60), (2, 25), V=128, sigma=1.5)
+    p, x, lx, ly, y = _setup(case)
+    B = p.B
+    ws = capi.alloc_workspace(p, DEV)
+    costs, loss, gx = torch.empty(B, device=DEV), torch.empty((), device=DEV), torch.empty_like(x)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        capi.loss_grad(p, x, lx, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=3)  # first use: not captured
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            capi.loss_grad(p, x, lx, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=3)
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(3)
+    for trial in range(2):
+        perm = rng.permutation(B)
+        lx2, ly2, y2 = case["lx"][perm], case["ly"][perm], case["y"][perm]
+        fresh = (rng.standard_normal(case["x"].shape) * 1.5).astype(np.float32)
+        x.copy_(torch.as_tensor(fresh))
+        lx.copy_(torch.as_tensor(lx2))
+        ly.copy_(torch.as_tensor(ly2))
+        y.copy_(torch.as_tensor(y2))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert capi.read_status(ws)[0] == 0
+        c64, d64 = oracle.fused(fresh, lx2, ly2, y2, 0, weights=np.full(B, 1.0 / B))
+        np.testing.assert_allclose(costs.cpu().numpy(), c64, rtol=1e-5)
+        assert abs(float(loss) - c64.mean()) <= 1e-5 * c64.mean()
+        assert np.abs(gx.cpu().numpy() - d64).max() <= 1e-5
