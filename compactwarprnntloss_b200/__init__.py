@@ -17,4 +17,7 @@ def __getattr__(name):
     if name in ("transducer_loss", "TransducerLoss", "compact_from_padded"):
         from . import loss
         return getattr(loss, name)
+    if name == "compact_joint":
+        from . import joint
+        return joint.compact_joint
     raise AttributeError(name)

@@ -27,7 +27,7 @@ EXPORTS = [
     "cwrnnt_scatter_backward", "cwrnnt_read_status", "cwrnnt_host_ctx_create", "cwrnnt_host_ctx_destroy",
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
-    "cwrnnt_scale_grad", "cwrnnt_pipeline_groups",
+    "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
 ]
 
 
@@ -67,6 +67,8 @@ def lib():
         L.cwrnnt_pipe_destroy.restype = None
         L.cwrnnt_loss_grad.argtypes = [vp, pp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp, vp, i32, vp, i32, vp]
         L.cwrnnt_scale_grad.argtypes = [pp, vp, vp, vp]
+        L.cwrnnt_joint_forward.argtypes = [pp, i32, vp, i32, vp, i32, vp, vp, vp, i64, vp, vp]
+        L.cwrnnt_joint_backward.argtypes = [pp, i32, vp, i32, vp, i32, vp, vp, vp, vp, i64, vp, vp, vp]
         L.cwrnnt_pipeline_groups.restype = i32
         L.cwrnnt_pipeline_groups.argtypes = [pp, i32]
         L.cwrnnt_pair_grads.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
@@ -250,6 +252,39 @@ def unpack_padded(compact: torch.Tensor, lx, ly, B: int, T: int, Up: int) -> tor
         check(lib().cwrnnt_unpack_padded(ctypes.byref(p), _ptr(compact), T, Up, _ptr(lx), _ptr(ly), _ptr(scratch), n,
                                          _ptr(out), _stream(compact.device)), "cwrnnt_unpack_padded")
     return out
+
+
+ACTIVATIONS = {None: 0, "none": 0, "relu": 1, "tanh": 2}
+
+
+def _joint_problem(enc, pred, lx, n_rows):
+    return Problem(n_rows, enc.size(2), lx.numel(), pred.size(1) - 1, pred.size(1) - 1, 0, dtype_code(enc.dtype), 0, 0)
+
+
+def joint_forward(enc: torch.Tensor, pred: torch.Tensor, lx, ly, n_rows: int, activation="tanh") -> torch.Tensor:
+    """act(enc[n,t] + pred[n,u]) for every lattice node, as compact rows [n_rows, H] (cwrnnt_joint_forward).
+    enc [B, t_max, H], pred [B, u_max1, H], contiguous, same dtype and device."""
+    out = torch.empty(n_rows, enc.size(2), dtype=enc.dtype, device=enc.device)
+    p = _joint_problem(enc, pred, lx, n_rows)
+    with torch.cuda.device(enc.device):
+        scratch = torch.empty(lib().cwrnnt_scatter_scratch_bytes(p.B), dtype=torch.uint8, device=enc.device)
+        check(lib().cwrnnt_joint_forward(ctypes.byref(p), ACTIVATIONS[activation], _ptr(enc), enc.size(1), _ptr(pred),
+                                         pred.size(1), _ptr(lx), _ptr(ly), _ptr(scratch), scratch.numel(), _ptr(out),
+                                         _stream(enc.device)), "cwrnnt_joint_forward")
+    return out
+
+
+def joint_backward(enc, pred, lx, ly, grad_out, activation="tanh"):
+    """(grad_enc like enc, grad_pred like pred) from grad_out [n_rows, H] (cwrnnt_joint_backward)."""
+    genc, gpred = torch.empty_like(enc), torch.empty_like(pred)
+    p = _joint_problem(enc, pred, lx, grad_out.size(0))
+    with torch.cuda.device(enc.device):
+        scratch = torch.empty(lib().cwrnnt_scatter_scratch_bytes(p.B), dtype=torch.uint8, device=enc.device)
+        check(lib().cwrnnt_joint_backward(ctypes.byref(p), ACTIVATIONS[activation], _ptr(enc), enc.size(1), _ptr(pred),
+                                          pred.size(1), _ptr(lx), _ptr(ly), _ptr(grad_out), _ptr(scratch),
+                                          scratch.numel(), _ptr(genc), _ptr(gpred), _stream(enc.device)),
+              "cwrnnt_joint_backward")
+    return genc, gpred
 
 
 def costs_static(p: Problem, x, lx, ly, y, costs, loss=None) -> None:

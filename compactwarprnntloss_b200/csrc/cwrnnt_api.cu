@@ -12,7 +12,7 @@ using namespace cwrnnt;
 // Side streams and events of a pipelined step (cwrnnt_loss_grad).
 struct cwrnnt_pipe {
     int device;
-    cudaStream_t alt;                  // second stream of the streaming kernels (odd groups; even ones use the caller's)
+    cudaStream_t alt;                  // streaming kernels of the odd groups (even ones: the caller's stream)
     cudaStream_t side[kMaxGroups];     // highest priority: the wavefront of group g
     cudaEvent_t gathered[kMaxGroups];  // recorded after the gather of range g
     cudaEvent_t solved[kMaxGroups];    // recorded on side[g] after the wavefront of group g
@@ -34,7 +34,8 @@ GroupPlan plan_groups(const cwrnnt_problem &p, int groups)
     // 0.628 unpipelined, 0.607 with 2, 0.609 with 8); 8 when the batch is a handful of long sequences, whose
     // wavefronts are the critical path (4 x [1250 x 300] x 512: 1.48 ms against 1.85, 1.64 with 4)
     const int large = p.B <= 8 ? 8 : 4;
-    const int want = groups > 0 ? groups : (bytes >= (int64_t(256) << 20) ? large : (bytes >= (int64_t(32) << 20) ? 2 : 1));
+    const int by_size = bytes >= (int64_t(256) << 20) ? large : (bytes >= (int64_t(32) << 20) ? 2 : 1);
+    const int want = groups > 0 ? groups : by_size;
     const int64_t kAlign = 512;  // whole tiles of every row shape of the streaming kernels (at most 64 runs of 8 rows)
     GroupPlan plan{1, p.n_rows > 0 ? p.n_rows : 1};
     if (want > 1 && p.n_rows > kAlign) {
@@ -367,6 +368,42 @@ int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact, int32_t t
                          cwrnnt_stream_t stream)
 {
     return pack_impl(p, false, compact, padded, t_max, u_max1, lx, ly, scratch, scratch_bytes, stream);
+}
+
+static int joint_impl(const cwrnnt_problem *p, int32_t activation, bool backward, const void *enc, int32_t t_max,
+                      const void *pred, int32_t u_max1, const int32_t *lx, const int32_t *ly, const void *grad_out,
+                      void *scratch, int64_t scratch_bytes, void *a, void *b, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (activation < CWRNNT_ACT_NONE || activation > CWRNNT_ACT_TANH) return CWRNNT_ERR_ARGUMENT;
+    if (p->B == 0) return CWRNNT_OK;
+    if (!lx || !ly || t_max < 1 || u_max1 < 1 || u_max1 < p->max_u + 1) return CWRNNT_ERR_ARGUMENT;
+    if (!enc || !pred || (backward ? (!a || !b || (p->n_rows > 0 && !grad_out)) : (p->n_rows > 0 && !a)))
+        return CWRNNT_ERR_ARGUMENT;
+    if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 8 != 0 || scratch_bytes < cwrnnt_scatter_scratch_bytes(p->B))
+        return CWRNNT_ERR_WORKSPACE;
+    cudaError_t e = launch_joint(*p, activation, backward, enc, t_max, pred, u_max1, lx, ly,
+                                 static_cast<int64_t *>(scratch), grad_out, a, b,
+                                 reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch(backward ? "joint_backward" : "joint_forward", e);
+}
+
+int cwrnnt_joint_forward(const cwrnnt_problem *p, int32_t activation, const void *enc, int32_t t_max, const void *pred,
+                         int32_t u_max1, const int32_t *lx, const int32_t *ly, void *scratch, int64_t scratch_bytes,
+                         void *out, cwrnnt_stream_t stream)
+{
+    return joint_impl(p, activation, false, enc, t_max, pred, u_max1, lx, ly, nullptr, scratch, scratch_bytes, out,
+                      nullptr, stream);
+}
+
+int cwrnnt_joint_backward(const cwrnnt_problem *p, int32_t activation, const void *enc, int32_t t_max,
+                          const void *pred, int32_t u_max1, const int32_t *lx, const int32_t *ly, const void *grad_out,
+                          void *scratch, int64_t scratch_bytes, void *grad_enc, void *grad_pred,
+                          cwrnnt_stream_t stream)
+{
+    return joint_impl(p, activation, true, enc, t_max, pred, u_max1, lx, ly, grad_out, scratch, scratch_bytes,
+                      grad_enc, grad_pred, stream);
 }
 
 int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream)

@@ -57,4 +57,10 @@ cudaError_t launch_scatter(const cwrnnt_problem &p, const void *grads, const voi
 cudaError_t launch_pack(const cwrnnt_problem &p, bool to_compact, const void *src, void *dst, int32_t t_max,
                         int32_t u_max1, const int32_t *lx, const int32_t *ly, int64_t *off_scratch, cudaStream_t s);
 
+// Joint broadcast-add into compact rows (forward: `out_or_grad_enc` = out [n_rows, H]) and its two reductions
+// (backward: grad_enc [B, t_max, H], grad_pred [B, u_max1, H] from grad_out [n_rows, H]); H = p.V.
+cudaError_t launch_joint(const cwrnnt_problem &p, int activation, bool backward, const void *enc, int32_t t_max,
+                         const void *pred, int32_t u_max1, const int32_t *lx, const int32_t *ly, int64_t *off_scratch,
+                         const void *grad_out, void *out_or_grad_enc, void *grad_pred, cudaStream_t s);
+
 }  // namespace cwrnnt

@@ -229,6 +229,30 @@ CWRNNT_API int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact
 CWRNNT_API int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream);
 
 /*
+ * The joint network's broadcast-add written straight into the compact layout - the producer in front of the loss:
+ *     out[off_n + t*(U_n+1) + u][:] = act(enc[n][t][:] + pred[n][u][:])
+ * from the padded encoder output enc [B, t_max, H] and predictor output pred [B, u_max1, H] (p->dtype; H = p->V,
+ * p->n_rows = sum_n lx[n]*(ly[n]+1); blank and flags of `p` are not used). The reference has no such function: its
+ * callers build the padded [N, T, U+1, H] joint tensor and compact that (test/test.py:34-48 defines the layout,
+ * cwarp_rnnt/__init__.py:52-59 compacts a padded 4-D input); here the padding is never materialised. A linear layer
+ * (a library GEMM) maps out [n_rows, H] to the logits [n_rows, V] that cwrnnt_forward / cwrnnt_loss_grad take.
+ * cwrnnt_joint_backward: grad_enc[n][t] = sum_u g*act', grad_pred[n][u] = sum_t g*act' with g = grad_out
+ * [n_rows, H]; both outputs are fully written (zero in the padding); deterministic summation order.
+ * scratch: cwrnnt_scatter_scratch_bytes(B) bytes, 8-byte aligned. Lengths that disagree with n_rows leave the forward
+ * output untouched and give zero gradients.
+ */
+#define CWRNNT_ACT_NONE 0
+#define CWRNNT_ACT_RELU 1
+#define CWRNNT_ACT_TANH 2
+CWRNNT_API int cwrnnt_joint_forward(const cwrnnt_problem *p, int32_t activation, const void *enc, int32_t t_max,
+                                    const void *pred, int32_t u_max1, const int32_t *lx, const int32_t *ly,
+                                    void *scratch, int64_t scratch_bytes, void *out, cwrnnt_stream_t stream);
+CWRNNT_API int cwrnnt_joint_backward(const cwrnnt_problem *p, int32_t activation, const void *enc, int32_t t_max,
+                                     const void *pred, int32_t u_max1, const int32_t *lx, const int32_t *ly,
+                                     const void *grad_out, void *scratch, int64_t scratch_bytes, void *grad_enc,
+                                     void *grad_pred, cwrnnt_stream_t stream);
+
+/*
  * Costs (and the reduced loss) without any caller workspace and without any allocation: for hosts that cannot call
  * cudaMalloc - a plug-in in a serving process whose framework owns all device memory, a foreign-language binding with
  * no device allocator to size a workspace with, a scoring loop that cannot afford the synchronisation an allocation

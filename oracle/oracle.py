@@ -189,3 +189,41 @@ def brute_force_cost(lp_blank, lp_label):
         logp += lp_blank[T - 1][U]
         total += math.exp(logp)
     return -math.log(total)
+
+
+_ACT = {
+    None: (lambda s: s, lambda s: np.ones_like(s)),
+    "none": (lambda s: s, lambda s: np.ones_like(s)),
+    "relu": (lambda s: np.maximum(s, 0.0), lambda s: (s > 0).astype(s.dtype)),
+    "tanh": (np.tanh, lambda s: 1.0 - np.tanh(s) ** 2),
+}
+
+
+def joint_compact(enc, pred, lx, ly, activation="tanh"):
+    """act(enc[n, t] + pred[n, u]) for every lattice node in the compact layout of the reference's test
+    (test/test.py:34-48: sequence n contributes its [:T_n, :U_n+1] block, rows in (t, u) order). Double precision.
+    enc [B, t_max, H], pred [B, u_max1, H] -> [sum_n T_n (U_n+1), H]."""
+    act, _ = _ACT[activation]
+    enc, pred = np.asarray(enc, np.float64), np.asarray(pred, np.float64)
+    rows = []
+    for n in range(len(lx)):
+        T, m = int(lx[n]), int(ly[n]) + 1
+        rows.append(act(enc[n, :T, None, :] + pred[n, None, :m, :]).reshape(T * m, -1))
+    return np.concatenate(rows, axis=0) if rows else np.zeros((0, enc.shape[2]))
+
+
+def joint_compact_backward(enc, pred, lx, ly, grad_out, activation="tanh"):
+    """Gradients of joint_compact w.r.t. enc and pred (zero in the padding), double precision."""
+    _, slope = _ACT[activation]
+    enc, pred = np.asarray(enc, np.float64), np.asarray(pred, np.float64)
+    g = np.asarray(grad_out, np.float64)
+    genc, gpred = np.zeros_like(enc), np.zeros_like(pred)
+    at = 0
+    for n in range(len(lx)):
+        T, m = int(lx[n]), int(ly[n]) + 1
+        s = enc[n, :T, None, :] + pred[n, None, :m, :]
+        d = g[at:at + T * m].reshape(T, m, -1) * slope(s)
+        genc[n, :T] = d.sum(axis=1)
+        gpred[n, :m] = d.sum(axis=0)
+        at += T * m
+    return genc, gpred
