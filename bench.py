@@ -317,6 +317,7 @@ def main():
 
     pipe = capi.Pipe(dev)
     n_groups = capi.pipeline_groups(p, args.groups)
+    main, comm = torch.cuda.current_stream(dev), torch.cuda.Stream(dev)
 
     def forward():
         if world == 1:
@@ -330,9 +331,13 @@ def main():
             capi.loss_grad(p, x, lxd, lyd, yd, ws, costs, loss, one, 0, gx, pipe=pipe, groups=args.groups)
         else:
             # the wavefront epilogue fills the global cost vector; one all-reduce is the whole exchange
+            # and it runs on a second stream as soon as the wavefronts are done, underneath the gradient kernels
             capi.loss_grad(p, x, lxd, lyd, yd, ws, costs, loss, one, 0, gx, pipe=pipe, groups=args.groups,
                            global_ids=ids_dev, n_global=B_global, cost_vector=vec)
-            dist.all_reduce(vec, op=dist.ReduceOp.SUM)
+            with torch.cuda.stream(comm):
+                pipe.wait_costs(comm)
+                dist.all_reduce(vec, op=dist.ReduceOp.SUM)
+            main.wait_stream(comm)
 
     def fence():
         if world > 1:

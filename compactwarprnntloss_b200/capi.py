@@ -28,6 +28,7 @@ EXPORTS = [
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
     "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
+    "cwrnnt_pipe_wait_costs",
 ]
 
 
@@ -65,6 +66,7 @@ def lib():
         L.cwrnnt_pipe_create.argtypes = [ctypes.POINTER(vp)]
         L.cwrnnt_pipe_destroy.argtypes = [vp]
         L.cwrnnt_pipe_destroy.restype = None
+        L.cwrnnt_pipe_wait_costs.argtypes = [vp, vp]
         L.cwrnnt_loss_grad.argtypes = [vp, pp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp, vp, i32, vp, i32, vp]
         L.cwrnnt_scale_grad.argtypes = [pp, vp, vp, vp]
         L.cwrnnt_joint_forward.argtypes = [pp, i32, vp, i32, vp, i32, vp, vp, vp, i64, vp, vp]
@@ -166,6 +168,11 @@ class Pipe:
         with torch.cuda.device(self.device):
             torch.cuda.current_stream()  # make sure the primary context exists
             check(lib().cwrnnt_pipe_create(ctypes.byref(self._h)), "cwrnnt_pipe_create")
+
+    def wait_costs(self, stream: torch.cuda.Stream) -> None:
+        """`stream` waits until the costs / loss / cost vector of the last loss_grad on this pipe are written (its
+        gradient kernels may still be running): the place to start an all-reduce of the cost vector."""
+        check(lib().cwrnnt_pipe_wait_costs(self._h, ctypes.c_void_p(stream.cuda_stream)), "cwrnnt_pipe_wait_costs")
 
     def close(self):
         if self._h:

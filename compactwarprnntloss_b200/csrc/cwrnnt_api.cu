@@ -17,6 +17,7 @@ struct cwrnnt_pipe {
     cudaEvent_t gathered[kMaxGroups];  // recorded after the gather of range g
     cudaEvent_t solved[kMaxGroups];    // recorded on side[g] after the wavefront of group g
     cudaEvent_t forked, joined;        // caller's stream -> alt at the start, alt -> caller's stream at the end
+    cudaEvent_t costs_ready;           // every wavefront of the last step is done: costs, loss, cost vector written
 };
 
 namespace {
@@ -169,6 +170,7 @@ int cwrnnt_pipe_create(cwrnnt_pipe **out)
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&pipe->alt, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->forked, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->joined, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->costs_ready, cudaEventDisableTiming);
     for (int g = 0; g < kMaxGroups && e == cudaSuccess; ++g) {
         // highest priority: a wavefront CTA must get onto an SM as soon as a CTA of the streaming kernels retires
         e = cudaStreamCreateWithPriority(&pipe->side[g], cudaStreamNonBlocking, greatest);
@@ -190,6 +192,7 @@ void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe)
     if (pipe->alt) cudaStreamDestroy(pipe->alt);
     if (pipe->forked) cudaEventDestroy(pipe->forked);
     if (pipe->joined) cudaEventDestroy(pipe->joined);
+    if (pipe->costs_ready) cudaEventDestroy(pipe->costs_ready);
     for (int g = 0; g < kMaxGroups; ++g) {
         if (pipe->side[g]) cudaStreamDestroy(pipe->side[g]);
         if (pipe->gathered[g]) cudaEventDestroy(pipe->gathered[g]);
@@ -254,6 +257,13 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
                    "wavefront");
         if (G > 1) CWRNNT_TRY(cudaEventRecord(pipe->solved[g], k2), "event");
     }
+    if (pipe) {
+        // costs, loss and the cost vector are final once every wavefront launch is done - before any gradient kernel
+        // has run. The event lets another stream (a collective on the cost vector) start from there.
+        cudaStream_t collect = G > 1 ? pipe->side[0] : s;
+        for (int g = 1; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(collect, pipe->solved[g], 0), "event");
+        CWRNNT_TRY(cudaEventRecord(pipe->costs_ready, collect), "event");
+    }
     for (int g = 0; g < G; ++g) {
         GradRows span{nullptr, 0};
         if (G > 1) {
@@ -271,6 +281,13 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
     }
 #undef CWRNNT_TRY
     return CWRNNT_OK;
+}
+
+int cwrnnt_pipe_wait_costs(cwrnnt_pipe *pipe, cwrnnt_stream_t stream)
+{
+    if (!pipe) return CWRNNT_ERR_ARGUMENT;
+    cudaError_t e = cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(stream), pipe->costs_ready, 0);
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("pipe_wait_costs", e);
 }
 
 int32_t cwrnnt_pipeline_groups(const cwrnnt_problem *p, int32_t groups)

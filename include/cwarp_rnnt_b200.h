@@ -168,6 +168,14 @@ CWRNNT_API int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, cons
                                 void *grad_x, const int32_t *global_ids, int32_t n_global, void *cost_vector,
                                 int32_t groups, cwrnnt_stream_t stream);
 
+/*
+ * Makes `stream` wait until the costs, the loss and the cost vector of the last cwrnnt_loss_grad issued through
+ * `pipe` are written - which is before its gradient kernels run. A sharded caller puts its all-reduce of the cost
+ * vector on a second stream behind this wait, so the collective runs underneath the gradient pass instead of after
+ * it. No counterpart in the reference (single GPU).
+ */
+CWRNNT_API int cwrnnt_pipe_wait_costs(cwrnnt_pipe *pipe, cwrnnt_stream_t stream);
+
 /* Number of sequence groups cwrnnt_loss_grad uses for this problem and `groups` argument (with a pipe); < 0 on bad
  * arguments. A step then launches 1 + 3 * groups kernels. No counterpart in the reference. */
 CWRNNT_API int32_t cwrnnt_pipeline_groups(const cwrnnt_problem *p, int32_t groups);

@@ -255,3 +255,30 @@ def test_pipelined_step_captured_in_a_cuda_graph(pipe, oracle):
         np.testing.assert_allclose(costs.cpu().numpy(), c64, rtol=1e-5)
         assert abs(float(loss) - c64.mean()) <= 1e-5 * c64.mean()
         assert np.abs(gx.cpu().numpy() - d64).max() <= 1e-5
+
+
+def test_costs_are_ready_before_the_gradient_pass(pipe):
+    """cwrnnt_pipe_wait_costs: a second stream that waits for the costs-ready event sees the final costs, loss and
+    cost vector (the place where a sharded caller starts its all-reduce), and the gradient still comes out right."""
+    case = ragged_case(23, 20, (20, 80), (3, 30), V=512)
+    args = _setup(case)
+    p, x, lx, ly, y = args
+    c0, l0, g0 = _two_calls(*args)
+    ws = capi.alloc_workspace(p, DEV)
+    costs = torch.full((p.B,), float("nan"), device=DEV)
+    loss = torch.full((), float("nan"), device=DEV)
+    vec = torch.full((p.B + 1,), float("nan"), device=DEV)
+    gx = torch.empty_like(x)
+    other = torch.cuda.Stream()
+    for groups in (1, 4):
+        capi.loss_grad(p, x, lx, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=groups, n_global=p.B,
+                       cost_vector=vec)
+        with torch.cuda.stream(other):
+            pipe.wait_costs(other)
+            seen_costs, seen_loss, seen_vec = costs.clone(), loss.clone(), vec.clone()
+        other.synchronize()
+        _same(seen_costs, c0)
+        _same(seen_loss, l0)
+        _same(seen_vec[:-1], c0)
+        torch.cuda.synchronize()
+        _same(gx, g0)
