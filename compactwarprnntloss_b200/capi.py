@@ -28,7 +28,7 @@ EXPORTS = [
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
     "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
-    "cwrnnt_pipe_wait_costs",
+    "cwrnnt_pipe_wait_costs", "cwrnnt_validate",
 ]
 
 
@@ -82,6 +82,7 @@ def lib():
         L.cwrnnt_unpack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_costs_static.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_read_status.argtypes = [vp, ctypes.POINTER(i32 * 4), vp]
+        L.cwrnnt_validate.argtypes = [pp, vp, vp, vp, vp, ctypes.POINTER(i32 * 4), vp]
         L.cwrnnt_host_ctx_create.argtypes = [ctypes.POINTER(vp)]
         L.cwrnnt_host_ctx_destroy.argtypes = [vp]
         L.cwrnnt_host_ctx_destroy.restype = None
@@ -308,6 +309,16 @@ def read_status(workspace: torch.Tensor):
     with torch.cuda.device(workspace.device):
         check(lib().cwrnnt_read_status(_ptr(workspace), ctypes.byref(out), _stream(workspace.device)),
               "cwrnnt_read_status")
+    return list(out)
+
+
+def validate(p: Problem, lx, ly, y):
+    """[status bits, first bad sequence, max(lx), max(ly)] from one small kernel and one short synchronisation."""
+    out = (ctypes.c_int32 * 4)()
+    with torch.cuda.device(lx.device):
+        scratch = torch.empty(4, dtype=torch.int32, device=lx.device)
+        check(lib().cwrnnt_validate(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(y) if y is not None and y.numel() else None,
+                                    _ptr(scratch), ctypes.byref(out), _stream(lx.device)), "cwrnnt_validate")
     return list(out)
 
 

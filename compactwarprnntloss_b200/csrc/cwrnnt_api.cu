@@ -1,5 +1,5 @@
 // C ABI of the engine (include/cwarp_rnnt_b200.h): argument checks, workspace carving, kernel sequencing.
-// No device allocation, no synchronisation (except cwrnnt_read_status), no exceptions; cwrnnt_pipe_create owns the
+// No device allocation, no synchronisation (except cwrnnt_read_status and cwrnnt_validate), no exceptions; cwrnnt_pipe_create owns the
 // only resources made here (side streams and events).
 #include <cstdio>
 #include <cstring>
@@ -385,6 +385,26 @@ int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact, int32_t t
                          cwrnnt_stream_t stream)
 {
     return pack_impl(p, false, compact, padded, t_max, u_max1, lx, ly, scratch, scratch_bytes, stream);
+}
+
+int cwrnnt_validate(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y, void *scratch,
+                    int32_t out[4], cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (!out) return CWRNNT_ERR_ARGUMENT;
+    out[0] = 0, out[1] = -1, out[2] = 0, out[3] = 0;
+    if (p->B == 0) {
+        if (p->n_rows != 0) out[0] = CWRNNT_ST_ROW_MISMATCH;
+        return CWRNNT_OK;
+    }
+    if (!lx || !ly || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
+    if (!scratch || reinterpret_cast<uintptr_t>(scratch) % 4 != 0) return CWRNNT_ERR_WORKSPACE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    cudaError_t e = launch_validate(*p, lx, ly, y, static_cast<int32_t *>(scratch), s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(out, scratch, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("validate", e);
 }
 
 static int joint_impl(const cwrnnt_problem *p, int32_t activation, bool backward, const void *enc, int32_t t_max,

@@ -11,6 +11,10 @@ void set_last_error(const char *text);
 cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
                         void *costs, cudaStream_t s, GroupPlan plan = GroupPlan{1, 1});
 
+// Lengths, row count and labels checked by one small kernel; four words into out_device (see cwrnnt_validate).
+cudaError_t launch_validate(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                            int32_t *out_device, cudaStream_t s);
+
 cudaError_t launch_offsets_only(const int32_t *lx, const int32_t *ly, int B, int max_u, int64_t *off, cudaStream_t s);
 
 // K1: row log-sum-exp + blank/label log-prob gather into the diagonal-major arrays, rows [row0, row1)

@@ -2,6 +2,8 @@
 // validation into the status words, and the longest-critical-path-first order used by the wavefront kernel.
 // Replaces the five ATen launches that build `offset` in the reference (cwarp_cuda.cpp:98-103) and the host-side
 // max().item() synchronisations (cwarp_cuda_rnnt_kernel.cu:395-396, cwarp_cuda_gather_kernel.cu:85-86).
+#include <climits>
+
 #include "cwrnnt_kernels.h"
 
 namespace cwrnnt {
@@ -107,6 +109,64 @@ cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_
     else
         prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
                                                       static_cast<float *>(costs), nullptr, plan);
+    return cudaGetLastError();
+}
+
+// Validation alone: the checks of K0 plus the label range, and the two maxima the reference asserts on the host.
+__global__ void __launch_bounds__(kPrepThreads)
+validate_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, const int32_t *__restrict__ y,
+                int y_stride, int B, int64_t n_rows, int max_u, int V, int32_t *__restrict__ out)
+{
+    __shared__ unsigned long long total;
+    __shared__ int bad_first, max_t, max_l, bad_label;
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        total = 0ull;
+        bad_first = 0x7fffffff;
+        max_t = INT_MIN;
+        max_l = INT_MIN;
+        bad_label = 0;
+    }
+    __syncthreads();
+    unsigned long long local = 0ull;
+    int lt = INT_MIN, ll = INT_MIN;
+    bool label_out = false;
+    for (int n = tid; n < B; n += kPrepThreads) {
+        int T = lx[n], U = ly[n];
+        lt = max(lt, T);
+        ll = max(ll, U);
+        if (T < 1 || U < 0 || U > max_u) {
+            atomicMin(&bad_first, n);
+            T = T < 1 ? 1 : T;
+            U = U < 0 ? 0 : (U > max_u ? max_u : U);
+        }
+        local += (unsigned long long)(T) * (unsigned long long)(U + 1);
+        for (int u = 0; u < U; ++u) {
+            const int k = y[int64_t(n) * y_stride + u];
+            label_out |= (k < 0 || k >= V);
+        }
+    }
+    atomicAdd(&total, local);
+    atomicMax(&max_t, lt);
+    atomicMax(&max_l, ll);
+    if (label_out) bad_label = 1;
+    __syncthreads();
+    if (tid == 0) {
+        int st = 0;
+        if (bad_first != 0x7fffffff) st |= CWRNNT_ST_BAD_LENGTH;
+        if (int64_t(total) != n_rows) st |= CWRNNT_ST_ROW_MISMATCH;
+        if (bad_label) st |= CWRNNT_ST_BAD_LABEL;
+        out[0] = st;
+        out[1] = bad_first != 0x7fffffff ? bad_first : -1;
+        out[2] = max_t;
+        out[3] = max_l;
+    }
+}
+
+cudaError_t launch_validate(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                            int32_t *out_device, cudaStream_t s)
+{
+    validate_kernel<<<1, kPrepThreads, 0, s>>>(lx, ly, y, p.y_stride, p.B, p.n_rows, p.max_u, p.V, out_device);
     return cudaGetLastError();
 }
 

@@ -180,6 +180,27 @@ void rnnt_scale_grad(torch::Tensor grad_x, const torch::Tensor &factor)
     check_status(cwrnnt_scale_grad(&p, grad_x.data_ptr(), f.data_ptr(), current_stream()), "cwrnnt_scale_grad");
 }
 
+// Input validation ahead of the heavy kernels: [status bits, first bad sequence, max(lx), max(ly)]; one short sync.
+std::vector<int64_t> rnnt_validate(const torch::Tensor &lx, const torch::Tensor &ys, const torch::Tensor &ly,
+                                   int64_t n_rows, int64_t V)
+{
+    CHECK_INPUT(lx, torch::ScalarType::Int);
+    CHECK_INPUT(ys, torch::ScalarType::Int);
+    CHECK_INPUT(ly, torch::ScalarType::Int);
+    TORCH_CHECK(ys.dim() == 2 && ys.size(0) == lx.size(0) && ly.size(0) == lx.size(0), "ys must be [N, Umax]");
+    const c10::cuda::CUDAGuard guard(lx.device());
+    cwrnnt_problem p{};
+    p.n_rows = n_rows;
+    p.V = static_cast<int32_t>(V);
+    p.B = static_cast<int32_t>(lx.size(0));
+    p.y_stride = p.max_u = static_cast<int32_t>(ys.size(1));
+    auto scratch = torch::empty({4}, lx.options());
+    int32_t st[4] = {0, 0, 0, 0};
+    check_status(cwrnnt_validate(&p, i32(lx), i32(ly), i32(ys), scratch.data_ptr(), st, current_stream()),
+                 "cwrnnt_validate");
+    return {st[0], st[1], st[2], st[3]};
+}
+
 // Device status words of a workspace: synchronises the current stream. [bits, first bad sequence, rows, 0].
 std::vector<int64_t> rnnt_status(const torch::Tensor &workspace)
 {
@@ -334,6 +355,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("_rnnt_loss_grad", &rnnt_loss_grad,
           "Pipelined forward + gradient for an upstream gradient of 1: (costs, loss, workspace, grad_x).");
     m.def("_rnnt_scale_grad", &rnnt_scale_grad, "In-place grad_x *= factor (device scalar); free when the factor is 1.");
+    m.def("_rnnt_validate", &rnnt_validate,
+          "Validates lengths, row count and labels: [bits, first bad sequence, max lx, max ly] (one short sync).");
     m.def("_rnnt_status", &rnnt_status, "Status words of a workspace (synchronises).");
     m.def("_pack_padded", &pack_padded, "Padded [N,T,U+1,V] -> compact [n_rows,V].");
     m.def("_unpack_padded", &unpack_padded, "Compact [n_rows,V] -> zero-padded [N,T,U+1,V].");

@@ -17,9 +17,11 @@ eager_grad          True (default): when ``x`` requires a gradient and the reduc
                     False: the gradient pass runs inside ``backward`` with the upstream gradient folded in - one pass
                     less when that gradient is not 1 (loss scaling), no overlap, and nothing computed if ``backward``
                     is never called.
-check               True (default): the reference's assertions, including the one that reads ``ly.max()`` on the host,
-                    plus a read of the device status word after the forward (one synchronisation). False: no host
-                    synchronisation at all; invalid lengths then surface as NaN costs.
+check               True (default): the reference's assertions, including ``y.size(1) == ly.max()``, plus checks the
+                    reference lacks (lengths, row count, label range). All of them that need device data come from
+                    one small validation kernel launched BEFORE the loss kernels and one short synchronisation
+                    (about 20 us), so the loss itself is never waited for. False: no host synchronisation at all;
+                    invalid lengths then surface as NaN costs.
 
 The CUDA extension is mandatory: importing this module without it raises ImportError (no CPU or PyTorch fallback).
 """
@@ -113,20 +115,30 @@ def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torc
     assert y.dim() == 2
     assert y.size(0) == lx.size(0)
     assert y.size(0) == ly.size(0)
-    if check:
-        assert y.size(1) == ly.max()
     assert blank >= 0 and blank < x.size(-1)
 
+    padded_frames = None
     if x.dim() == 4:
         print("WARNING: it seems your input is not compact... would try to compact the input.")
         N, T, Up, V = x.size()
         assert y.size(1) + 1 == Up
-        if check:
-            assert lx.max() == T
+        padded_frames = T
         x = compact_from_padded(x, lx, ly)
 
     # x: (STU, V)
     assert x.dim() == 2
+
+    if check:
+        # bits, first bad sequence, max(lx), max(ly): everything the assertions below need from the device
+        st = core._rnnt_validate(lx, y.contiguous(), ly, x.size(0), x.size(1))
+        assert y.size(1) == st[3]                                  # reference: y.size(1) == ly.max()
+        assert padded_frames is None or st[2] == padded_frames      # reference: lx.max() == T for 4-D input
+        if st[0] & core.ST_BAD_LENGTH:
+            raise ValueError(f"invalid length at sequence {st[1]}: need lx >= 1 and 0 <= ly <= y.size(1)")
+        if st[0] & core.ST_ROW_MISMATCH:
+            raise ValueError(f"x has {x.size(0)} rows but sum(lx*(ly+1)) is different")
+        if st[0] & core.ST_BAD_LABEL:
+            raise ValueError("a label lies outside [0, V)")
 
     flags = 0
     if fused_log_softmax:
@@ -140,7 +152,8 @@ def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torc
     elif not (reduction == "none" or reduction is None):
         raise ValueError
 
-    costs, loss = _TransLoss.apply(x.contiguous(), lx, y.contiguous(), ly, blank, flags, mean_denominator, check,
+    # validated above: the autograd function itself does not read the device status back
+    costs, loss = _TransLoss.apply(x.contiguous(), lx, y.contiguous(), ly, blank, flags, mean_denominator, False,
                                    eager_grad)
     return loss if reduction in ("mean", "sum") else costs
 

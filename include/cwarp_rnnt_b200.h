@@ -237,6 +237,18 @@ CWRNNT_API int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact
 CWRNNT_API int cwrnnt_read_status(const void *workspace, int32_t out[4], cwrnnt_stream_t stream);
 
 /*
+ * Input validation by itself, ahead of the heavy kernels: one small kernel over lx, ly and y, four words copied to
+ * HOST memory `out`, one wait on the stream (about 20 us). out[0] = CWRNNT_ST_BAD_LENGTH / ROW_MISMATCH / BAD_LABEL
+ * bits, out[1] = first sequence with an invalid length (-1 if none), out[2] = max_n lx[n], out[3] = max_n ly[n].
+ * Covers the reference's host-side assertions that read device data (`y.size(1) == ly.max()`, `lx.max() == T`,
+ * cwarp_rnnt/__init__.py:49,58) and the checks it lacks, without waiting for the loss itself: a caller that validates
+ * first can then launch cwrnnt_forward / cwrnnt_loss_grad and never synchronise. `scratch`: 16 bytes of device
+ * memory, 4-byte aligned.
+ */
+CWRNNT_API int cwrnnt_validate(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                               void *scratch, int32_t out[4], cwrnnt_stream_t stream);
+
+/*
  * The joint network's broadcast-add written straight into the compact layout - the producer in front of the loss:
  *     out[off_n + t*(U_n+1) + u][:] = act(enc[n][t][:] + pred[n][u][:])
  * from the padded encoder output enc [B, t_max, H] and predictor output pred [B, u_max1, H] (p->dtype; H = p->V,

@@ -82,3 +82,5 @@ def test_pipelined_step_rejects_bad_arguments_before_any_launch():
     args[-2] = 9
     assert L.cwrnnt_loss_grad(None, ctypes.byref(p), *args) == 1       # more groups than supported
     assert L.cwrnnt_scale_grad(ctypes.byref(p), None, None, None) == 1
+    out = (ctypes.c_int32 * 4)()
+    assert L.cwrnnt_validate(ctypes.byref(p), None, None, None, None, ctypes.byref(out), None) == 1

@@ -249,3 +249,26 @@ def test_pack_and_unpack_padded_through_the_c_abi(dtype, V):
     for n in range(N):
         assert torch.equal(back[n, :lx[n], :ly[n] + 1], xp[n, :lx[n], :ly[n] + 1])
         assert back[n, lx[n]:].abs().sum() == 0 and back[n, :, ly[n] + 1:].abs().sum() == 0
+
+
+def test_validate_reports_lengths_rows_labels_and_maxima():
+    """cwrnnt_validate: the device-side facts behind the reference's host assertions, from one small kernel."""
+    from compactwarprnntloss_b200 import capi
+    case = ragged_case(5, 300, (1, 40), (0, 17), V=33)
+    x, lx, y, ly = _tensors(case)
+    p = capi.make_problem(x, lx, y, 0, capi.FUSED_LOG_SOFTMAX)
+    assert capi.validate(p, lx, ly, y) == [0, -1, int(case["lx"].max()), int(case["ly"].max())]
+    bad = y.clone()
+    n = int(np.argmax(case["ly"]))
+    bad[n, 0] = 33                                        # one label out of range, inside the used part of its row
+    assert capi.validate(p, lx, ly, bad)[0] == capi.ST_BAD_LABEL
+    bad = y.clone()
+    short = int(np.argmin(case["ly"]))
+    bad[short, int(case["ly"][short]):] = -7                # padding beyond ly[n] is never looked at
+    assert capi.validate(p, lx, ly, bad)[0] == 0
+    lx2 = lx.clone()
+    lx2[7] = 0
+    st = capi.validate(p, lx2, ly, y)
+    assert st[0] & capi.ST_BAD_LENGTH and st[1] == 7 and st[0] & capi.ST_ROW_MISMATCH
+    q = capi.make_problem(x[:-1], lx, y, 0, capi.FUSED_LOG_SOFTMAX)
+    assert capi.validate(q, lx, ly, y)[0] == capi.ST_ROW_MISMATCH
