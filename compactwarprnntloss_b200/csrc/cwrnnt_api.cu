@@ -276,8 +276,10 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
                    "grad");
     }
     if (G > 1) {
+        // join: everything issued on alt, and the collecting side stream (every wavefront stream is behind it)
         CWRNNT_TRY(cudaEventRecord(pipe->joined, pipe->alt), "event");
         CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->joined, 0), "event");
+        CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->costs_ready, 0), "event");
     }
 #undef CWRNNT_TRY
     return CWRNNT_OK;

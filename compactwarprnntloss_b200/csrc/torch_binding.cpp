@@ -8,7 +8,6 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
-#include <mutex>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -133,12 +132,11 @@ torch::Tensor rnnt_backward(const torch::Tensor &xs, const torch::Tensor &lx, co
     return gx;
 }
 
-// Side streams of the pipelined step, one set per device, created on first use and kept for the life of the process.
+// Side streams of the pipelined step: one set per device and host thread (a pipe serves one call at a time), created
+// on first use and kept for the life of the thread's process.
 cwrnnt_pipe *pipe_of(int device_index)
 {
-    static std::mutex lock;
-    static std::vector<cwrnnt_pipe *> pipes;
-    std::lock_guard<std::mutex> hold(lock);
+    static thread_local std::vector<cwrnnt_pipe *> pipes;
     if (device_index >= static_cast<int>(pipes.size())) pipes.resize(device_index + 1, nullptr);
     if (!pipes[device_index]) check_status(cwrnnt_pipe_create(&pipes[device_index]), "cwrnnt_pipe_create");
     return pipes[device_index];
