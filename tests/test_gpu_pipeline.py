@@ -304,3 +304,38 @@ def test_random_shapes_against_the_two_call_path(pipe):
         groups = int(rng.integers(0, 9))
         c1, l1, g1, _ = _one_call(pipe, *args, groups=groups)
         assert torch.equal(c0, c1) and torch.equal(l0, l1) and torch.equal(g0, g1), (trial, B, V, dtype, groups)
+
+
+def test_many_tiny_sequences_in_groups(pipe):
+    """4500 sequences (beyond the longest-first sort, 9000 wavefront CTAs per launch, four launches sharing one
+    completion ticket)."""
+    case = ragged_case(32, 4500, (1, 4), (0, 3), V=8)
+    args = _setup(case)
+    c0, l0, g0 = _two_calls(*args)
+    for groups in (4, 8):
+        c1, l1, g1, _ = _one_call(pipe, *args, groups=groups)
+        _same(c0, c1)
+        _same(l0, l1)
+        _same(g0, g1)
+
+
+def test_invalid_lengths_stop_every_group(pipe):
+    """A row count that disagrees with the lengths is fatal: no group's kernels run, the costs are NaN, the status
+    says why, and the pipe is usable again afterwards."""
+    case = ragged_case(6, 30, (10, 40), (2, 12), V=64)
+    p, x, lx, ly, y = _setup(case)
+    lx_bad = lx.clone()
+    lx_bad[3] += 1
+    ws = capi.alloc_workspace(p, DEV)
+    costs = torch.zeros(p.B, device=DEV)
+    loss = torch.zeros((), device=DEV)
+    gx = torch.full_like(x, 5.0)
+    capi.loss_grad(p, x, lx_bad, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=4)
+    torch.cuda.synchronize()
+    st = capi.read_status(ws)
+    assert st[0] & capi.ST_ROW_MISMATCH
+    assert bool(torch.isnan(costs).all()) and bool((gx == 5.0).all())
+    c0, l0, g0 = _two_calls(p, x, lx, ly, y)
+    c1, l1, g1, _ = _one_call(pipe, p, x, lx, ly, y, groups=4)
+    _same(c0, c1)
+    _same(g0, g1)
