@@ -35,7 +35,9 @@ GroupPlan plan_groups(const cwrnnt_problem &p, int groups)
     // 0.628 unpipelined, 0.607 with 2, 0.609 with 8); 8 when the batch is a handful of long sequences, whose
     // wavefronts are the critical path (4 x [1250 x 300] x 512: 1.48 ms against 1.85, 1.64 with 4)
     const int large = p.B <= 8 ? 8 : 4;
-    const int by_size = bytes >= (int64_t(256) << 20) ? large : (bytes >= (int64_t(32) << 20) ? 2 : 1);
+    // below 256 MB no grouping: the wavefront chain is then the critical path, and it runs slower next to the
+    // streaming kernels than alone (230 MB of ragged rows: 0.416 ms with two groups against 0.379 ms with one)
+    const int by_size = bytes >= (int64_t(256) << 20) ? large : 1;
     const int want = groups > 0 ? groups : by_size;
     const int64_t kAlign = 512;  // whole tiles of every row shape of the streaming kernels (at most 64 runs of 8 rows)
     GroupPlan plan{1, p.n_rows > 0 ? p.n_rows : 1};

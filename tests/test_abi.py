@@ -60,7 +60,8 @@ def test_pipeline_group_plan_is_host_arithmetic():
 
     assert groups(314340, 1024, 32) == 4             # 1.29 GB, ordinary batch
     assert groups(1420000, 512, 4) == 8              # a handful of long sequences
-    assert groups(40000, 256, 40) == 2               # 41 MB
+    assert groups(40000, 256, 40) == 1               # 41 MB: below 256 MB the step is not cut up
+    assert groups(100000, 1024, 32) == 4             # 410 MB
     assert groups(1500, 64, 4) == 1                  # small: no grouping
     assert groups(314340, 1024, 32, forced=3) == 3
     assert groups(300, 1024, 32, forced=8) == 1      # fewer rows than one aligned range
