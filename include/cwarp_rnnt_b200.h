@@ -146,16 +146,17 @@ CWRNNT_API int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int
  * during the forward call and backward only scales them (cwarp_rnnt/__init__.py:10-29, cwarp_cuda.cpp:84-136) - and,
  * with CWRNNT_FUSED_LOG_SOFTMAX, the caller's log_softmax forward and backward.
  * The rows are cut into `groups` ranges; group g = the sequences whose last row lies in range g. On the caller's
- * stream: K0, gather of range 0..G-1, then the gradient of group 0..G-1. On the pipe's high-priority side streams:
- * the alpha/beta wavefront of group g as soon as range g is gathered. The wavefront (a chain of T+U dependent steps on
- * a few SMs) thereby runs underneath the two bandwidth-bound passes instead of between them. Everything is joined
- * back into `stream` before the call returns (event waits, nothing blocks the host), so results are ordered on
- * `stream` exactly like those of cwrnnt_forward + cwrnnt_backward; they are bit-identical to that pair's.
+ * stream and one more stream of the pipe, alternating: K0, the gather of range 0..G-1, then the gradient of group
+ * 0..G-1. On the pipe's high-priority side streams: the alpha/beta wavefront of group g as soon as ranges 0..g are
+ * gathered. The wavefront (a chain of T+U dependent steps on a few SMs) thereby runs underneath the two
+ * bandwidth-bound passes instead of between them. Everything is joined back into `stream` before the call returns
+ * (event waits, nothing blocks the host), so results are ordered on `stream` exactly like those of cwrnnt_forward +
+ * cwrnnt_backward; they are bit-identical to that pair's.
  *   pipe        side streams and events, from cwrnnt_pipe_create on the same device; one call at a time per pipe.
  *               NULL runs the same work on `stream` alone without overlap.
  *   grad_costs / grad_costs_stride / grad_x   as cwrnnt_backward (NULL grad_costs: upstream gradient 1)
  *   global_ids / n_global / cost_vector       as cwrnnt_forward_sharded, or NULL / 0 / NULL
- *   groups      0 = chosen from the size of x; 1..8 to force
+ *   groups      0 = chosen from the size of x (one group, i.e. no overlap, below 256 MB of logits); 1..8 to force
  * CWRNNT_COSTS_ONLY is refused (use cwrnnt_forward). The workspace ends up in the same state as after
  * cwrnnt_forward, so cwrnnt_backward / cwrnnt_pair_grads / cwrnnt_export_alpha_beta may follow.
  */
