@@ -5,6 +5,8 @@ Sub-modules:
   capi      ctypes view of the C ABI (include/cwarp_rnnt_b200.h)
   sharding  sequence sharding across GPUs and the cost-vector exchange
   synth     seeded synthetic workloads of the benchmark configurations
+  joint     `compact_joint` - the joint network's broadcast-add written directly as compact rows
+  graphs    `GraphedStep` - a whole training step of the loss as one replayed CUDA graph per shape bucket
   build     in-tree build of the native parts
 
 Importing the package itself is light and works on a machine without a GPU; `loss` and `capi.lib()` raise if the
@@ -17,6 +19,9 @@ def __getattr__(name):
     if name in ("transducer_loss", "TransducerLoss", "compact_from_padded"):
         from . import loss
         return getattr(loss, name)
+    if name == "GraphedStep":
+        from . import graphs
+        return graphs.GraphedStep
     if name == "compact_joint":
         from . import joint
         return joint.compact_joint

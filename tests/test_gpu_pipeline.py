@@ -339,3 +339,24 @@ def test_invalid_lengths_stop_every_group(pipe):
     c1, l1, g1, _ = _one_call(pipe, p, x, lx, ly, y, groups=4)
     _same(c0, c1)
     _same(g0, g1)
+
+
+def test_graphed_step_bucket(oracle):
+    """GraphedStep: one graph per (rows, sequences, label width) bucket, replayed on batches whose lengths differ."""
+    from compactwarprnntloss_b200 import GraphedStep
+    case = ragged_case(51, 10, (5, 50), (1, 20), V=96, sigma=1.5)
+    B, n_rows = 10, case["x"].shape[0]
+    bucket = GraphedStep(n_rows, 96, B, int(case["ly"].max()) + 3, dtype=torch.float32, device=DEV, groups=3)
+    rng = np.random.default_rng(7)
+    for trial in range(3):
+        perm = rng.permutation(B)
+        lx, ly, y = case["lx"][perm], case["ly"][perm], case["y"][perm]
+        x = (rng.standard_normal(case["x"].shape) * 1.5).astype(np.float32)
+        loss, costs, grad = bucket.step(torch.as_tensor(x).to(DEV), torch.as_tensor(lx).to(DEV),
+                                        torch.as_tensor(ly).to(DEV), torch.as_tensor(y).to(DEV))
+        torch.cuda.synchronize()
+        assert bucket.status()[0] == 0
+        c64, d64 = oracle.fused(x, lx, ly, y, 0, weights=np.full(B, 1.0 / B))
+        np.testing.assert_allclose(costs.cpu().numpy(), c64, rtol=1e-5)
+        assert abs(float(loss) - c64.mean()) <= 1e-5 * c64.mean()
+        assert np.abs(grad.cpu().numpy() - d64).max() <= 1e-5
