@@ -28,7 +28,7 @@ EXPORTS = [
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
     "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
-    "cwrnnt_pipe_wait_costs", "cwrnnt_validate",
+    "cwrnnt_pipe_wait_costs", "cwrnnt_validate", "cwrnnt_validate_async", "cwrnnt_static_status", "cwrnnt_fill_costs",
 ]
 
 
@@ -81,8 +81,11 @@ def lib():
         L.cwrnnt_pack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_unpack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_costs_static.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
+        L.cwrnnt_fill_costs.argtypes = [pp, vp, vp, vp, vp, vp, vp]
+        L.cwrnnt_static_status.argtypes = [ctypes.POINTER(i32 * 4), vp]
         L.cwrnnt_read_status.argtypes = [vp, ctypes.POINTER(i32 * 4), vp]
         L.cwrnnt_validate.argtypes = [pp, vp, vp, vp, vp, ctypes.POINTER(i32 * 4), vp]
+        L.cwrnnt_validate_async.argtypes = [pp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_host_ctx_create.argtypes = [ctypes.POINTER(vp)]
         L.cwrnnt_host_ctx_destroy.argtypes = [vp]
         L.cwrnnt_host_ctx_destroy.restype = None
@@ -304,6 +307,21 @@ def costs_static(p: Problem, x, lx, ly, y, costs, loss=None) -> None:
                                         _ptr(loss), _stream(x.device)), "cwrnnt_costs_static")
 
 
+def fill_costs(p: Problem, lx, ll_alpha, ll_beta, costs, status) -> None:
+    """costs[n] = -guarded(ll_alpha[n], ll_beta[n]); ORs ST_FWD_BWD_GAP into the device int32 word `status`."""
+    with torch.cuda.device(lx.device):
+        check(lib().cwrnnt_fill_costs(ctypes.byref(p), _ptr(lx), _ptr(ll_alpha), _ptr(ll_beta), _ptr(costs),
+                                      _ptr(status), _stream(lx.device)), "cwrnnt_fill_costs")
+
+
+def static_status(device):
+    """Status words of the last costs_static call on `device` (synchronises its current stream)."""
+    out = (ctypes.c_int32 * 4)()
+    with torch.cuda.device(device):
+        check(lib().cwrnnt_static_status(ctypes.byref(out), _stream(device)), "cwrnnt_static_status")
+    return list(out)
+
+
 def read_status(workspace: torch.Tensor):
     out = (ctypes.c_int32 * 4)()
     with torch.cuda.device(workspace.device):
@@ -320,6 +338,17 @@ def validate(p: Problem, lx, ly, y):
         check(lib().cwrnnt_validate(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(y) if y is not None and y.numel() else None,
                                     _ptr(scratch), ctypes.byref(out), _stream(lx.device)), "cwrnnt_validate")
     return list(out)
+
+
+def validate_async(p: Problem, lx, ly, y, out_pinned: torch.Tensor, scratch: torch.Tensor) -> None:
+    """Queues the validation on the current stream and returns; `out_pinned` (pinned int32[4] CPU tensor) holds
+    [status bits, first bad sequence, max(lx), max(ly)] once the stream - or an event recorded after this call - is
+    waited for. `scratch`: int32[4] on the device, kept alive by the caller until then."""
+    assert out_pinned.is_pinned() and out_pinned.dtype == torch.int32 and out_pinned.numel() >= 4
+    with torch.cuda.device(lx.device):
+        check(lib().cwrnnt_validate_async(ctypes.byref(p), _ptr(lx), _ptr(ly),
+                                          _ptr(y) if y is not None and y.numel() else None, _ptr(scratch),
+                                          _ptr(out_pinned), _stream(lx.device)), "cwrnnt_validate_async")
 
 
 class HostPipeline:

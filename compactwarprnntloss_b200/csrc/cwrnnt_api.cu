@@ -120,7 +120,9 @@ static int forward_impl(const cwrnnt_problem *p, const void *x, const int32_t *l
     if (p->B == 0) return CWRNNT_OK;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if ((e = launch_prep(*p, lx, ly, w, costs, s)) != cudaSuccess) return fail_launch("prep", e);
+    e = launch_prep(*p, lx, ly, w, costs, s, GroupPlan{1, 1}, loss, shard ? shard->cost_vector : nullptr,
+                    shard ? shard->n_global : 0);
+    if (e != cudaSuccess) return fail_launch("prep", e);
     if ((e = launch_gather(*p, x, lx, ly, y, w, s)) != cudaSuccess) return fail_launch("gather", e);
     if ((e = launch_wavefront(*p, lx, ly, w, costs, loss, shard, s)) != cudaSuccess) return fail_launch("wavefront", e);
     return CWRNNT_OK;
@@ -238,7 +240,7 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
 #define CWRNNT_TRY(call, what) \
     if ((e = (call)) != cudaSuccess) return fail_launch(what, e)
     auto rows_stream = [&](int g) { return (G > 1 && (g & 1)) ? pipe->alt : s; };
-    CWRNNT_TRY(launch_prep(*p, lx, ly, w, costs, s, plan), "prep");
+    CWRNNT_TRY(launch_prep(*p, lx, ly, w, costs, s, plan, loss, cost_vector, n_global), "prep");
     if (G > 1) {
         CWRNNT_TRY(cudaEventRecord(pipe->forked, s), "event");
         CWRNNT_TRY(cudaStreamWaitEvent(pipe->alt, pipe->forked, 0), "event");
@@ -267,12 +269,13 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
         CWRNNT_TRY(cudaEventRecord(pipe->costs_ready, collect), "event");
     }
     for (int g = 0; g < G; ++g) {
-        GradRows span{nullptr, 0};
+        GradRows span{nullptr, 0, 0, 0};
         if (G > 1) {
             CWRNNT_TRY(cudaStreamWaitEvent(rows_stream(g), pipe->solved[g], 0), "event");
             // a group holds the sequences that END in its range, so it is about one range long, give or take a
             // sequence: the grid is sized for one range and a longer group is finished by the same CTAs
-            span = GradRows{w.bounds + g, plan.range_rows};
+            const int64_t row0 = g * plan.range_rows;
+            span = GradRows{w.bounds + g, plan.range_rows, row0, g == G - 1 ? p->n_rows : row0 + plan.range_rows};
         }
         CWRNNT_TRY(launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x, rows_stream(g), span),
                    "grad");
@@ -341,6 +344,17 @@ int cwrnnt_export_alpha_beta(const cwrnnt_problem *p, const int32_t *lx, const i
     return e == cudaSuccess ? CWRNNT_OK : fail_launch("export_alpha_beta", e);
 }
 
+int cwrnnt_fill_costs(const cwrnnt_problem *p, const int32_t *lx, const double *ll_alpha, const double *ll_beta,
+                      void *costs, int32_t *status, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    if (!lx || !ll_beta || !costs || !status) return CWRNNT_ERR_ARGUMENT;
+    cudaError_t e = launch_fill_costs(*p, lx, ll_alpha, ll_beta, costs, status, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("fill_costs", e);
+}
+
 int64_t cwrnnt_scatter_scratch_bytes(int32_t B) { return B < 0 ? -1 : align_up(8 * (int64_t(B) + 1), 256); }
 
 int cwrnnt_scatter_backward(const cwrnnt_problem *p, const void *grads, const void *grad_costs, const int32_t *lx,
@@ -391,15 +405,14 @@ int cwrnnt_unpack_padded(const cwrnnt_problem *p, const void *compact, int32_t t
     return pack_impl(p, false, compact, padded, t_max, u_max1, lx, ly, scratch, scratch_bytes, stream);
 }
 
-int cwrnnt_validate(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y, void *scratch,
-                    int32_t out[4], cwrnnt_stream_t stream)
+static int validate_impl(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                         void *scratch, int32_t out[4], cwrnnt_stream_t stream, bool wait)
 {
     int st = check_problem(p);
     if (st) return st;
     if (!out) return CWRNNT_ERR_ARGUMENT;
-    out[0] = 0, out[1] = -1, out[2] = 0, out[3] = 0;
     if (p->B == 0) {
-        if (p->n_rows != 0) out[0] = CWRNNT_ST_ROW_MISMATCH;
+        out[0] = p->n_rows != 0 ? CWRNNT_ST_ROW_MISMATCH : 0, out[1] = -1, out[2] = 0, out[3] = 0;
         return CWRNNT_OK;
     }
     if (!lx || !ly || (p->max_u > 0 && !y)) return CWRNNT_ERR_ARGUMENT;
@@ -407,8 +420,20 @@ int cwrnnt_validate(const cwrnnt_problem *p, const int32_t *lx, const int32_t *l
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t e = launch_validate(*p, lx, ly, y, static_cast<int32_t *>(scratch), s);
     if (e == cudaSuccess) e = cudaMemcpyAsync(out, scratch, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e == cudaSuccess && wait) e = cudaStreamSynchronize(s);
     return e == cudaSuccess ? CWRNNT_OK : fail_launch("validate", e);
+}
+
+int cwrnnt_validate(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y, void *scratch,
+                    int32_t out[4], cwrnnt_stream_t stream)
+{
+    return validate_impl(p, lx, ly, y, scratch, out, stream, true);
+}
+
+int cwrnnt_validate_async(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                          void *scratch, int32_t out[4], cwrnnt_stream_t stream)
+{
+    return validate_impl(p, lx, ly, y, scratch, out, stream, false);
 }
 
 static int joint_impl(const cwrnnt_problem *p, int32_t activation, bool backward, const void *enc, int32_t t_max,

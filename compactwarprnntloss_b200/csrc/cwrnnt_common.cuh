@@ -335,4 +335,18 @@ __device__ __forceinline__ double sequence_scale(int flags, int T)
     return (flags & CWRNNT_AVERAGE_FRAMES) ? 1.0 / double(T) : 1.0;
 }
 
+// The reference's forward/backward consistency guard (cwarp_cuda_rnnt_kernel.cu:350-366): `a` = alpha(T-1,U) + the
+// final blank, `b` = beta(0,0) are the same log-likelihood computed from both ends. When they differ by more than 1e-3
+// relative to the larger one the reference prints a warning and uses their mean; here the mean is used and `gap` is
+// raised (it becomes the CWRNNT_ST_FWD_BWD_GAP status bit). Otherwise beta's value stands.
+__device__ __forceinline__ double guarded_loglik(double a, double b, bool &gap)
+{
+    const double big = fmax(a, b);
+    if (fabs(a - b) / fabs(big) > 1e-3) {
+        gap = true;
+        return 0.5 * (a + b);
+    }
+    return b;
+}
+
 }  // namespace cwrnnt

@@ -93,6 +93,36 @@ scatter_kernel(int64_t n_rows, int V, int B, const int32_t *__restrict__ lx, con
     }
 }
 
+// costs[n] = -guarded(ll_alpha[n], ll_beta[n]) (* 1/T_n under CWRNNT_AVERAGE_FRAMES): the cost step of the wavefront's
+// epilogue on its own, from caller-supplied log-likelihoods (reference fill_cost_kernel,
+// cwarp_cuda_rnnt_kernel.cu:334-367). status[0] receives CWRNNT_ST_FWD_BWD_GAP when the guard fires.
+template <typename CostT>
+__global__ void __launch_bounds__(kStreamThreads)
+fill_costs_kernel(int B, int flags, const int32_t *__restrict__ lx, const double *__restrict__ ll_alpha,
+                  const double *__restrict__ ll_beta, CostT *__restrict__ costs, int32_t *__restrict__ status)
+{
+    const int n = blockIdx.x * kStreamThreads + threadIdx.x;
+    if (n >= B) return;
+    bool gap = false;
+    const double ll = ll_alpha ? guarded_loglik(ll_alpha[n], ll_beta[n], gap) : ll_beta[n];
+    if (gap) atomicOr(status, CWRNNT_ST_FWD_BWD_GAP);
+    costs[n] = CostT(-ll * sequence_scale(flags, lx[n]));
+}
+
+cudaError_t launch_fill_costs(const cwrnnt_problem &p, const int32_t *lx, const double *ll_alpha,
+                              const double *ll_beta, void *costs, int32_t *status, cudaStream_t s)
+{
+    if (p.B == 0) return cudaSuccess;
+    const int grid = (p.B + kStreamThreads - 1) / kStreamThreads;
+    if (p.dtype == CWRNNT_F64)
+        fill_costs_kernel<double><<<grid, kStreamThreads, 0, s>>>(p.B, p.flags, lx, ll_alpha, ll_beta,
+                                                                  static_cast<double *>(costs), status);
+    else
+        fill_costs_kernel<float><<<grid, kStreamThreads, 0, s>>>(p.B, p.flags, lx, ll_alpha, ll_beta,
+                                                                 static_cast<float *>(costs), status);
+    return cudaGetLastError();
+}
+
 static int stream_grid(int64_t items, int per_cta)
 {
     int64_t t = (items + per_cta - 1) / per_cta;

@@ -8,8 +8,9 @@
 //     grad[r][k] = w_n * ( p_k * (occ_b + occ_l) - [k == blank] occ_b - [k == y_u] occ_l ).
 // That one pass replaces: the in-place scaling of the saved pair gradients (cwarp_cuda_rnnt_kernel.cu:512-521), the
 // zero fill of [STU,V] (cwarp_cuda.cpp:134), scatter_grad_cuda_kernel (cwarp_cuda_gather_kernel.cu:52-74) and the
-// caller's log_softmax backward. Each row is read once (128-bit loads, evict-first) and written once (128-bit
-// streaming stores); the per-row scalars (lse, alpha, two betas) are 32 bytes against V*sizeof(element).
+// caller's log_softmax backward. Each row is read once and written once with plain 128-bit loads and stores (the
+// evict-first variants measured 7 % slower); the per-row scalars (lse, alpha, two betas) are 32 bytes against
+// V*sizeof(element).
 //
 // Log-prob mode: the reference's own result, zeros plus the two sparse terms; the input rows are not read at all.
 //
@@ -18,6 +19,19 @@
 #include "cwrnnt_rowmap.cuh"
 
 namespace cwrnnt {
+
+// Invalid lengths (fatal status): nothing upstream ran, so the rows of this launch are filled with NaN instead of being
+// left as they were - a caller that never reads the status then sees the failure in the gradient itself. `rows` holds
+// the host-known range of the launch (for a sequence group: its nominal row range; the ranges tile the matrix).
+template <typename T>
+__device__ __noinline__ void fill_rows_nan(T *__restrict__ gx, int V, const RowRange &rows)
+{
+    const int64_t n = (rows.end - rows.begin) * int64_t(V);
+    T *base = gx + rows.begin * int64_t(V);
+    const T nan = Elt<T>::from_acc(typename Elt<T>::acc(NAN));
+    for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x)
+        base[i] = nan;
+}
 
 __device__ __forceinline__ double occupancy(double e, float) { return double(expf(float(e))); }
 __device__ __forceinline__ double occupancy(double e, double) { return exp(e); }
@@ -59,7 +73,10 @@ grad_rows_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRange ro
     using CostT = typename E::cost;
     constexpr int VE = E::VE;
     constexpr int GPC = kStreamThreads / LPR;
-    if (w.status[0] & CWRNNT_ST_FATAL) return;
+    if (w.status[0] & CWRNNT_ST_FATAL) {
+        fill_rows_nan(gx, V, rows);
+        return;
+    }
 
     const int gl = threadIdx.x % LPR;
     const int nvec = V / VE;
@@ -131,7 +148,10 @@ grad_rows_long_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowRan
     constexpr int VE = E::VE;
     constexpr int NV = 8;
     constexpr int kWarps = kStreamThreads / 32;
-    if (w.status[0] & CWRNNT_ST_FATAL) return;
+    if (w.status[0] & CWRNNT_ST_FATAL) {
+        fill_rows_nan(gx, V, rows);
+        return;
+    }
 
     const int lane = threadIdx.x & 31;
     const int nvec = V / VE;
@@ -199,7 +219,10 @@ grad_rows_generic_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, Row
     using E = Elt<T>;
     using A = typename E::acc;
     using CostT = typename E::cost;
-    if (w.status[0] & CWRNNT_ST_FATAL) return;
+    if (w.status[0] & CWRNNT_ST_FATAL) {
+        fill_rows_nan(gx, V, rows);
+        return;
+    }
     const int lane = threadIdx.x & 31;
     int64_t row0, row1;
     rows.resolve(row0, row1);
@@ -243,7 +266,10 @@ grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowR
     using A = typename E::acc;
     using CostT = typename E::cost;
     constexpr int VE = E::VE;
-    if (w.status[0] & CWRNNT_ST_FATAL) return;
+    if (w.status[0] & CWRNNT_ST_FATAL) {
+        fill_rows_nan(gx, V, rows);
+        return;
+    }
     const int lane = threadIdx.x & 31;
     int64_t row0, row1;
     rows.resolve(row0, row1);
@@ -291,7 +317,8 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     if (p.n_rows == 0) return cudaSuccess;
     // rows of this launch: everything, or a sequence group whose bounds only the device knows; the grid is then
     // sized for span.grid_rows rows (the kernels cope with a longer range, more slowly)
-    const RowRange rows{0, p.n_rows, span.device_range};
+    const RowRange rows{span.device_range ? span.nominal_begin : 0, span.device_range ? span.nominal_end : p.n_rows,
+                        span.device_range};
     const int64_t n_rows = span.device_range ? (span.grid_rows < p.n_rows ? span.grid_rows : p.n_rows) : p.n_rows;
     if (n_rows <= 0) return cudaSuccess;
     constexpr int VE = Elt<T>::VE;

@@ -50,6 +50,24 @@ struct cwrnnt_host_ctx {
         }                                                                                          \
     } while (0)
 
+// Waits for everything queued on the context's streams; the results are ignored (the caller is already failing).
+static void drain(cwrnnt_host_ctx *ctx)
+{
+    cudaStreamSynchronize(ctx->s_up);
+    cudaStreamSynchronize(ctx->s_run);
+    cudaStreamSynchronize(ctx->s_down);
+}
+
+#define CKD(call)                                                                                  \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) {                                                                   \
+            std::snprintf(ctx->err, sizeof ctx->err, "%s: %s", #call, cudaGetErrorString(e_));     \
+            drain(ctx);                                                                            \
+            return CWRNNT_ERR_LAUNCH;                                                              \
+        }                                                                                          \
+    } while (0)
+
 extern "C" {
 
 int cwrnnt_host_ctx_create(cwrnnt_host_ctx **out)
@@ -198,14 +216,16 @@ int cwrnnt_loss_grad_host(cwrnnt_host_ctx *ctx, const cwrnnt_problem *p, const v
         ctx->run_ev.push_back(b);
     }
 
-    // ---- small inputs first, on the upload stream
+    // ---- small inputs first, on the upload stream. From here on copies from and into the caller's host buffers are in
+    // flight: a failure drains the three streams before returning (CKD), so that the caller may free or reuse those
+    // buffers and the context's slots are idle for the next call.
     int32_t *d_lx = ctx->lens, *d_ly = ctx->lens + B, *d_y = ctx->lens + 2 * int64_t(B);
-    CK(cudaMemcpyAsync(d_lx, lx_host, size_t(B) * 4, cudaMemcpyHostToDevice, ctx->s_up));
-    CK(cudaMemcpyAsync(d_ly, ly_host, size_t(B) * 4, cudaMemcpyHostToDevice, ctx->s_up));
+    CKD(cudaMemcpyAsync(d_lx, lx_host, size_t(B) * 4, cudaMemcpyHostToDevice, ctx->s_up));
+    CKD(cudaMemcpyAsync(d_ly, ly_host, size_t(B) * 4, cudaMemcpyHostToDevice, ctx->s_up));
     if (p->y_stride > 0)
-        CK(cudaMemcpyAsync(d_y, y_host, size_t(B) * p->y_stride * 4, cudaMemcpyHostToDevice, ctx->s_up));
+        CKD(cudaMemcpyAsync(d_y, y_host, size_t(B) * p->y_stride * 4, cudaMemcpyHostToDevice, ctx->s_up));
     if (grad_costs_host)
-        CK(cudaMemcpyAsync(ctx->gc, grad_costs_host, (grad_costs_stride ? size_t(B) : 1) * cs, cudaMemcpyHostToDevice,
+        CKD(cudaMemcpyAsync(ctx->gc, grad_costs_host, (grad_costs_stride ? size_t(B) : 1) * cs, cudaMemcpyHostToDevice,
                            ctx->s_up));
 
     // ---- the pipeline
@@ -214,10 +234,10 @@ int cwrnnt_loss_grad_host(cwrnnt_host_ctx *ctx, const cwrnnt_problem *p, const v
     for (size_t c = 0; c < chunks.size(); ++c) {
         const Chunk &ch = chunks[c];
         Slot &sl = ctx->slot[c % kSlots];
-        if (c >= size_t(kSlots)) CK(cudaStreamWaitEvent(ctx->s_up, sl.free_ev, 0));
-        CK(cudaMemcpyAsync(sl.x, xh + ch.row0 * row_bytes, size_t(ch.rows * row_bytes), cudaMemcpyHostToDevice,
+        if (c >= size_t(kSlots)) CKD(cudaStreamWaitEvent(ctx->s_up, sl.free_ev, 0));
+        CKD(cudaMemcpyAsync(sl.x, xh + ch.row0 * row_bytes, size_t(ch.rows * row_bytes), cudaMemcpyHostToDevice,
                            ctx->s_up));
-        CK(cudaEventRecord(ctx->up_ev[c], ctx->s_up));
+        CKD(cudaEventRecord(ctx->up_ev[c], ctx->s_up));
 
         cwrnnt_problem sub = *p;
         sub.n_rows = ch.rows;
@@ -227,30 +247,36 @@ int cwrnnt_loss_grad_host(cwrnnt_host_ctx *ctx, const cwrnnt_problem *p, const v
         const char *gc_c = grad_costs_host
                                ? static_cast<const char *>(ctx->gc) + (grad_costs_stride ? size_t(ch.seq0) * cs : 0)
                                : nullptr;
-        CK(cudaStreamWaitEvent(ctx->s_run, ctx->up_ev[c], 0));
+        CKD(cudaStreamWaitEvent(ctx->s_run, ctx->up_ev[c], 0));
         int st = cwrnnt_forward(&sub, sl.x, d_lx + ch.seq0, d_ly + ch.seq0, d_y + int64_t(ch.seq0) * p->y_stride,
                                 sl.ws, ctx->cap_ws_bytes, costs_c, nullptr,
                                 reinterpret_cast<cwrnnt_stream_t>(ctx->s_run));
-        if (st) return st;
+        if (st) {
+            drain(ctx);
+            return st;
+        }
         if (want_grad) {
             st = cwrnnt_backward(&sub, sl.x, d_lx + ch.seq0, d_ly + ch.seq0, d_y + int64_t(ch.seq0) * p->y_stride,
                                  sl.ws, gc_c, grad_costs_stride, sl.g, reinterpret_cast<cwrnnt_stream_t>(ctx->s_run));
-            if (st) return st;
+            if (st) {
+            drain(ctx);
+            return st;
         }
-        CK(cudaMemcpyAsync(ctx->status_h + 4 * c, sl.ws, 16, cudaMemcpyDeviceToHost, ctx->s_run));
-        CK(cudaEventRecord(ctx->run_ev[c], ctx->s_run));
+        }
+        CKD(cudaMemcpyAsync(ctx->status_h + 4 * c, sl.ws, 16, cudaMemcpyDeviceToHost, ctx->s_run));
+        CKD(cudaEventRecord(ctx->run_ev[c], ctx->s_run));
 
-        CK(cudaStreamWaitEvent(ctx->s_down, ctx->run_ev[c], 0));
+        CKD(cudaStreamWaitEvent(ctx->s_down, ctx->run_ev[c], 0));
         if (want_grad)
-            CK(cudaMemcpyAsync(gh + ch.row0 * row_bytes, sl.g, size_t(ch.rows * row_bytes), cudaMemcpyDeviceToHost,
+            CKD(cudaMemcpyAsync(gh + ch.row0 * row_bytes, sl.g, size_t(ch.rows * row_bytes), cudaMemcpyDeviceToHost,
                                ctx->s_down));
-        CK(cudaEventRecord(sl.free_ev, ctx->s_down));
+        CKD(cudaEventRecord(sl.free_ev, ctx->s_down));
     }
-    CK(cudaStreamWaitEvent(ctx->s_down, ctx->run_ev[chunks.size() - 1], 0));
-    CK(cudaMemcpyAsync(costs_host, ctx->costs, size_t(B) * cs, cudaMemcpyDeviceToHost, ctx->s_down));
-    CK(cudaStreamSynchronize(ctx->s_down));
-    CK(cudaStreamSynchronize(ctx->s_run));
-    CK(cudaStreamSynchronize(ctx->s_up));
+    CKD(cudaStreamWaitEvent(ctx->s_down, ctx->run_ev[chunks.size() - 1], 0));
+    CKD(cudaMemcpyAsync(costs_host, ctx->costs, size_t(B) * cs, cudaMemcpyDeviceToHost, ctx->s_down));
+    CKD(cudaStreamSynchronize(ctx->s_down));
+    CKD(cudaStreamSynchronize(ctx->s_run));
+    CKD(cudaStreamSynchronize(ctx->s_up));
 
     // ---- status and reduction on the host (B numbers)
     if (status_out) {

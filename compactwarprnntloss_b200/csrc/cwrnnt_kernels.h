@@ -7,9 +7,12 @@ namespace cwrnnt {
 // Text returned by cwrnnt_last_error() on the calling thread.
 void set_last_error(const char *text);
 
-// K0: offsets, validation, longest-first order, first row of every sequence group of `plan`. 1 CTA.
+// K0: offsets, validation, longest-first order, first row of every sequence group of `plan`. 1 CTA. On invalid
+// lengths it writes NaN to costs, to *loss (when a reduction flag is set) and to the n_global + 1 entries of a sharded
+// run's cost vector; either pointer may be null.
 cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                        void *costs, cudaStream_t s, GroupPlan plan = GroupPlan{1, 1});
+                        void *costs, cudaStream_t s, GroupPlan plan = GroupPlan{1, 1}, void *loss = nullptr,
+                        void *cost_vector = nullptr, int n_global = 0);
 
 // Lengths, row count and labels checked by one small kernel; four words into out_device (see cwrnnt_validate).
 cudaError_t launch_validate(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const int32_t *y,
@@ -36,14 +39,16 @@ cudaError_t launch_wavefront(const cwrnnt_problem &p, const int32_t *lx, const i
                              GroupPlan plan = GroupPlan{1, 1}, int group = 0);
 
 // K3: dense gradient in one streaming pass, over all rows or over the rows device_range[0] .. device_range[1]
-// (a sequence group; the pair lives in device memory, the grid is sized for grid_rows rows).
+// (a sequence group; the pair lives in device memory, the grid is sized for grid_rows rows). nominal_begin/end: the
+// host-known row range this launch stands for, used only to fill the gradient with NaN after a fatal input error.
 struct GradRows {
     const int64_t *device_range;
     int64_t grid_rows;
+    int64_t nominal_begin, nominal_end;
 };
 cudaError_t launch_grad(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
                         const int32_t *y, const Workspace &w, const void *grad_costs, int32_t gc_stride, void *grad_x,
-                        cudaStream_t s, const GradRows &span = GradRows{nullptr, 0});
+                        cudaStream_t s, const GradRows &span = GradRows{nullptr, 0, 0, 0});
 
 // grad_x *= *factor (a device scalar of the costs' type); returns at once on the device when the factor is 1.
 cudaError_t launch_scale(const cwrnnt_problem &p, void *grad_x, const void *factor, cudaStream_t s);
@@ -55,6 +60,10 @@ cudaError_t launch_export_ab(const cwrnnt_problem &p, const int32_t *lx, const i
                              int32_t t_max, int32_t u_max1, void *alphas, void *betas, cudaStream_t s);
 cudaError_t launch_scatter(const cwrnnt_problem &p, const void *grads, const void *grad_costs, const int32_t *lx,
                            const int32_t *ly, const int32_t *y, int64_t *off_scratch, void *dense, cudaStream_t s);
+
+// Costs from per-sequence log-likelihoods with the forward/backward guard (ll_alpha may be null: no guard).
+cudaError_t launch_fill_costs(const cwrnnt_problem &p, const int32_t *lx, const double *ll_alpha,
+                              const double *ll_beta, void *costs, int32_t *status, cudaStream_t s);
 
 // Padded [B, t_max, u_max1, V] <-> compact [n_rows, V] (to_compact: src padded, dst compact; else the transpose,
 // zero-filling the padding).

@@ -14,7 +14,8 @@ constexpr int kSortLimit = 4096;  // rank sort is O(B^2 / threads); beyond this 
 template <typename CostT>
 __global__ void __launch_bounds__(kPrepThreads)
 prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int B, int64_t n_rows, int max_u,
-            Workspace w, CostT *__restrict__ costs, int64_t *off_only, GroupPlan plan)
+            Workspace w, CostT *__restrict__ costs, CostT *__restrict__ loss, CostT *__restrict__ cost_vec,
+            int n_global, int64_t *off_only, GroupPlan plan)
 {
     __shared__ int64_t part[kPrepThreads];
     __shared__ int bad_first;
@@ -54,7 +55,9 @@ prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int 
         run += int64_t(T) * (int64_t(U) + 1);
     }
     const int64_t total = part[kPrepThreads - 1];
-    if (tid == 0) off[B] = total;
+    // offsets alone (the copy kernels around the loss): a clamped length must not pass for a consistent batch, so the
+    // total is replaced by -1, which no row count equals, and every consumer of these offsets leaves
+    if (tid == 0) off[B] = (off_only && bad_first != 0x7fffffff) ? -1 : total;
     if (off_only) return;
 
     int st = 0;
@@ -68,8 +71,13 @@ prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int 
         *w.ticket = 0u;
     }
     if (st & CWRNNT_ST_FATAL) {
-        // nothing downstream runs; make that visible in the result
+        // nothing downstream runs; make that visible in every result the caller may read without asking for the
+        // status: costs, the reduced loss and - for a sharded run - the whole cost vector, so that the all-reduce
+        // carries the failure to every rank (the gradient kernels fill their rows with NaN themselves)
         for (int n = tid; n < B; n += kPrepThreads) costs[n] = CostT(NAN);
+        if (tid == 0 && loss) *loss = CostT(NAN);
+        if (cost_vec)
+            for (int i = tid; i <= n_global; i += kPrepThreads) cost_vec[i] = CostT(NAN);
         return;
     }
 
@@ -100,15 +108,19 @@ prep_kernel(const int32_t *__restrict__ lx, const int32_t *__restrict__ ly, int 
 }
 
 cudaError_t launch_prep(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
-                        void *costs, cudaStream_t s, GroupPlan plan)
+                        void *costs, cudaStream_t s, GroupPlan plan, void *loss, void *cost_vector,
+                        int n_global)
 {
     if (plan.count < 1 || plan.count > kMaxGroups || plan.range_rows < 1) return cudaErrorInvalidValue;
+    if (!(p.flags & (CWRNNT_REDUCE_MEAN | CWRNNT_REDUCE_SUM))) loss = nullptr;  // written only under a reduction
     if (p.dtype == CWRNNT_F64)
         prep_kernel<double><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
-                                                       static_cast<double *>(costs), nullptr, plan);
+                                                       static_cast<double *>(costs), static_cast<double *>(loss),
+                                                       static_cast<double *>(cost_vector), n_global, nullptr, plan);
     else
         prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, p.B, p.n_rows, p.max_u, w,
-                                                      static_cast<float *>(costs), nullptr, plan);
+                                                      static_cast<float *>(costs), static_cast<float *>(loss),
+                                                      static_cast<float *>(cost_vector), n_global, nullptr, plan);
     return cudaGetLastError();
 }
 
@@ -174,7 +186,8 @@ cudaError_t launch_validate(const cwrnnt_problem &p, const int32_t *lx, const in
 cudaError_t launch_offsets_only(const int32_t *lx, const int32_t *ly, int B, int max_u, int64_t *off, cudaStream_t s)
 {
     Workspace none{};
-    prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, B, 0, max_u, none, nullptr, off, GroupPlan{1, 1});
+    prep_kernel<float><<<1, kPrepThreads, 0, s>>>(lx, ly, B, 0, max_u, none, nullptr, nullptr, nullptr, 0, off,
+                                                  GroupPlan{1, 1});
     return cudaGetLastError();
 }
 

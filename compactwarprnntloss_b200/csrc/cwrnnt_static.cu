@@ -88,12 +88,43 @@ extern "C" int cwrnnt_costs_static(const cwrnnt_problem *p, const void *x, const
     static_header_clear_kernel<<<1, 32, 0, s>>>();
     const char *what = "static header clear";
     e = cudaGetLastError();
-    if (e == cudaSuccess) what = "prep", e = launch_prep(q, lx, ly, w, costs, s);
+    if (e == cudaSuccess) what = "prep", e = launch_prep(q, lx, ly, w, costs, s, GroupPlan{1, 1}, loss);
     if (e == cudaSuccess) what = "gather", e = launch_gather(q, x, lx, ly, y, w, s);
     if (e == cudaSuccess) what = "wavefront", e = launch_wavefront(q, lx, ly, w, costs, loss, nullptr, s);
     if (e != cudaSuccess) {
         char msg[160];
         std::snprintf(msg, sizeof msg, "cwrnnt_costs_static %s: %s", what, cudaGetErrorString(e));
+        set_last_error(msg);
+        return CWRNNT_ERR_LAUNCH;
+    }
+    return CWRNNT_OK;
+}
+
+// The status words of the last cwrnnt_costs_static on the current device (the scratch is private to the library, so
+// cwrnnt_read_status cannot reach them). Copies 16 bytes to HOST memory `out` and waits for the stream; allocates
+// nothing. Before the first cwrnnt_costs_static on this device there is nothing to report: all-clear words come back.
+extern "C" int cwrnnt_static_status(int32_t out[4], cwrnnt_stream_t stream)
+{
+    if (!out) return CWRNNT_ERR_ARGUMENT;
+    out[0] = 0, out[1] = -1, out[2] = 0, out[3] = 0;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_last_error("cwrnnt_static_status: cannot identify the current device");
+        return CWRNNT_ERR_LAUNCH;
+    }
+    void *base = nullptr;
+    {
+        std::lock_guard<std::mutex> hold(g_setup_lock);
+        base = g_scratch_addr[dev];
+    }
+    if (!base) return CWRNNT_OK;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    e = cudaMemcpyAsync(out, base, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        char msg[160];
+        std::snprintf(msg, sizeof msg, "cwrnnt_static_status: %s", cudaGetErrorString(e));
         set_last_error(msg);
         return CWRNNT_ERR_LAUNCH;
     }

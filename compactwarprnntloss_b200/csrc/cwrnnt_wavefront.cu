@@ -329,13 +329,9 @@ __device__ __forceinline__ void finalize_if_last(const WaveArgs<CostT> &g, int n
     for (int i = threadIdx.x; i < g.B; i += n_active) {
         double b = __ldcg(w.ll_beta + i);
         if (g.n_dirs == 2) {
-            // forward/backward consistency guard of the reference (cwarp_cuda_rnnt_kernel.cu:350-366)
-            const double a = __ldcg(w.ll_alpha + i);
-            const double big = fmax(a, b);
-            if (fabs(a - b) / fabs(big) > 1e-3) {
-                b = 0.5 * (a + b);
-                atomicOr(w.status, CWRNNT_ST_FWD_BWD_GAP);
-            }
+            bool gap = false;
+            b = guarded_loglik(__ldcg(w.ll_alpha + i), b, gap);
+            if (gap) atomicOr(w.status, CWRNNT_ST_FWD_BWD_GAP);
         }
         const double c = -b * sequence_scale(g.flags, g.lx[i]);
         g.costs[i] = CostT(c);

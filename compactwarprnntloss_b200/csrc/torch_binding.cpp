@@ -199,6 +199,29 @@ std::vector<int64_t> rnnt_validate(const torch::Tensor &lx, const torch::Tensor 
     return {st[0], st[1], st[2], st[3]};
 }
 
+// The same validation queued without waiting: returns the four words as a pinned host tensor that is filled once the
+// current stream has passed this point. The caller records an event, queues the loss kernels, then waits on the event.
+torch::Tensor rnnt_validate_begin(const torch::Tensor &lx, const torch::Tensor &ys, const torch::Tensor &ly,
+                                  int64_t n_rows, int64_t V)
+{
+    CHECK_INPUT(lx, torch::ScalarType::Int);
+    CHECK_INPUT(ys, torch::ScalarType::Int);
+    CHECK_INPUT(ly, torch::ScalarType::Int);
+    TORCH_CHECK(ys.dim() == 2 && ys.size(0) == lx.size(0) && ly.size(0) == lx.size(0), "ys must be [N, Umax]");
+    const c10::cuda::CUDAGuard guard(lx.device());
+    cwrnnt_problem p{};
+    p.n_rows = n_rows;
+    p.V = static_cast<int32_t>(V);
+    p.B = static_cast<int32_t>(lx.size(0));
+    p.y_stride = p.max_u = static_cast<int32_t>(ys.size(1));
+    auto scratch = torch::empty({4}, lx.options());  // freed stream-ordered by the caching allocator
+    auto out = torch::empty({4}, torch::TensorOptions().dtype(torch::kInt32).pinned_memory(true));
+    check_status(cwrnnt_validate_async(&p, i32(lx), i32(ly), i32(ys), scratch.data_ptr(), out.data_ptr<int32_t>(),
+                                       current_stream()),
+                 "cwrnnt_validate_async");
+    return out;
+}
+
 // Device status words of a workspace: synchronises the current stream. [bits, first bad sequence, rows, 0].
 std::vector<int64_t> rnnt_status(const torch::Tensor &workspace)
 {
@@ -355,6 +378,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("_rnnt_scale_grad", &rnnt_scale_grad, "In-place grad_x *= factor (device scalar); free when the factor is 1.");
     m.def("_rnnt_validate", &rnnt_validate,
           "Validates lengths, row count and labels: [bits, first bad sequence, max lx, max ly] (one short sync).");
+    m.def("_rnnt_validate_begin", &rnnt_validate_begin,
+          "Queues the validation and returns a pinned int32[4] tensor filled once the current stream gets there.");
     m.def("_rnnt_status", &rnnt_status, "Status words of a workspace (synchronises).");
     m.def("_pack_padded", &pack_padded, "Padded [N,T,U+1,V] -> compact [n_rows,V].");
     m.def("_unpack_padded", &unpack_padded, "Compact [n_rows,V] -> zero-padded [N,T,U+1,V].");

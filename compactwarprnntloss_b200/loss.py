@@ -19,9 +19,10 @@ eager_grad          True (default): when ``x`` requires a gradient and the reduc
                     is never called.
 check               True (default): the reference's assertions, including ``y.size(1) == ly.max()``, plus checks the
                     reference lacks (lengths, row count, label range). All of them that need device data come from
-                    one small validation kernel launched BEFORE the loss kernels and one short synchronisation
-                    (about 20 us), so the loss itself is never waited for. False: no host synchronisation at all;
-                    invalid lengths then surface as NaN costs.
+                    one small validation kernel queued BEFORE the loss kernels; the host waits for its four words
+                    only after the loss kernels are queued as well, so neither the GPU nor the loss waits for the
+                    check, and a bad batch still raises before a loss is returned. False: no host synchronisation at
+                    all; invalid lengths then surface as NaN costs, NaN loss and a NaN gradient.
 
 The CUDA extension is mandatory: importing this module without it raises ImportError (no CPU or PyTorch fallback).
 """
@@ -117,28 +118,41 @@ def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torc
     assert y.size(0) == ly.size(0)
     assert blank >= 0 and blank < x.size(-1)
 
-    padded_frames = None
+    def _raise_on(st, rows):
+        if st[0] & core.ST_BAD_LENGTH:
+            raise ValueError(f"invalid length at sequence {st[1]}: need lx >= 1 and 0 <= ly <= y.size(1)")
+        if st[0] & core.ST_ROW_MISMATCH:
+            raise ValueError(f"x has {rows} rows but sum(lx*(ly+1)) is different")
+        if st[0] & core.ST_BAD_LABEL:
+            raise ValueError("a label lies outside [0, V)")
+
+    y = y.contiguous()
+    pending = None  # (pinned status words, event): a validation that is queued but not yet waited for
     if x.dim() == 4:
         print("WARNING: it seems your input is not compact... would try to compact the input.")
         N, T, Up, V = x.size()
         assert y.size(1) + 1 == Up
-        padded_frames = T
-        x = compact_from_padded(x, lx, ly)
+        # the compaction reads the lengths on the host anyway (row count), so this path validates them first, with a
+        # wait, before any kernel indexes the padded tensor with them
+        n_rows = int((lx.long() * (ly.long() + 1)).sum())
+        if check:
+            st = core._rnnt_validate(lx, y, ly, n_rows, V)
+            assert y.size(1) == st[3]                               # reference: y.size(1) == ly.max()
+            assert st[2] == T                                       # reference: lx.max() == T for 4-D input
+            _raise_on(st, n_rows)
+        x = _PackPadded.apply(x, lx, ly, n_rows)
+    elif check:
+        # bits, first bad sequence, max(lx), max(ly): everything the assertions below need from the device, queued
+        # AHEAD of the loss kernels and waited for only after they are queued too - the kernels protect themselves
+        # (invalid lengths: they return at once and the results are NaN; labels are clamped), so the GPU does not
+        # idle for the round trip and a bad batch still raises before a loss is returned
+        words = core._rnnt_validate_begin(lx, y, ly, x.size(0), x.size(1))
+        done = torch.cuda.Event()
+        done.record(torch.cuda.current_stream(lx.device))
+        pending = (words, done)
 
     # x: (STU, V)
     assert x.dim() == 2
-
-    if check:
-        # bits, first bad sequence, max(lx), max(ly): everything the assertions below need from the device
-        st = core._rnnt_validate(lx, y.contiguous(), ly, x.size(0), x.size(1))
-        assert y.size(1) == st[3]                                  # reference: y.size(1) == ly.max()
-        assert padded_frames is None or st[2] == padded_frames      # reference: lx.max() == T for 4-D input
-        if st[0] & core.ST_BAD_LENGTH:
-            raise ValueError(f"invalid length at sequence {st[1]}: need lx >= 1 and 0 <= ly <= y.size(1)")
-        if st[0] & core.ST_ROW_MISMATCH:
-            raise ValueError(f"x has {x.size(0)} rows but sum(lx*(ly+1)) is different")
-        if st[0] & core.ST_BAD_LABEL:
-            raise ValueError("a label lies outside [0, V)")
 
     flags = 0
     if fused_log_softmax:
@@ -152,9 +166,14 @@ def transducer_loss(x: torch.Tensor, lx: torch.Tensor, y: torch.Tensor, ly: torc
     elif not (reduction == "none" or reduction is None):
         raise ValueError
 
-    # validated above: the autograd function itself does not read the device status back
-    costs, loss = _TransLoss.apply(x.contiguous(), lx, y.contiguous(), ly, blank, flags, mean_denominator, False,
-                                   eager_grad)
+    # validated here: the autograd function itself does not read the device status back
+    costs, loss = _TransLoss.apply(x.contiguous(), lx, y, ly, blank, flags, mean_denominator, False, eager_grad)
+    if pending is not None:
+        words, done = pending
+        done.synchronize()
+        st = words.tolist()
+        assert y.size(1) == st[3]                                   # reference: y.size(1) == ly.max()
+        _raise_on(st, x.size(0))
     return loss if reduction in ("mean", "sum") else costs
 
 

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CWRNNT_ABI_VERSION 2
+#define CWRNNT_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define CWRNNT_API __attribute__((visibility("default")))
@@ -203,6 +203,19 @@ CWRNNT_API int cwrnnt_export_alpha_beta(const cwrnnt_problem *p, const int32_t *
                              int32_t t_max, int32_t u_max1, void *alphas, void *betas, cwrnnt_stream_t stream);
 
 /*
+ * The cost step by itself: costs[n] = -ll[n] (divided by T_n under CWRNNT_AVERAGE_FRAMES) from per-sequence
+ * log-likelihoods held in DEVICE double arrays - ll_alpha[n] = alpha(T-1,U) + the final blank, ll_beta[n] = beta(0,0).
+ * Replaces fill_cost_kernel (cwarp_cuda_rnnt_kernel.cu:334-367) including its consistency guard: where the two differ
+ * by more than 1e-3 relative, their mean is used and CWRNNT_ST_FWD_BWD_GAP is OR-ed into the DEVICE word *status (the
+ * reference prints from the device instead, :361). ll_alpha NULL: no guard, as in the costs-only path (:575). Only B,
+ * dtype (type of costs) and the CWRNNT_AVERAGE_FRAMES flag of `p` are used. cwrnnt_forward runs the same step inside
+ * the wavefront kernel's epilogue; this entry serves callers that hold alpha/beta from elsewhere, and the tests of
+ * the guard.
+ */
+CWRNNT_API int cwrnnt_fill_costs(const cwrnnt_problem *p, const int32_t *lx, const double *ll_alpha,
+                                 const double *ll_beta, void *costs, int32_t *status, cwrnnt_stream_t stream);
+
+/*
  * Reference-shaped backward from saved pair gradients: dense[r][blank] = grads[r][0]*g_n, dense[r][y] =
  * grads[r][1]*g_n, zero elsewhere. Replaces cwarp_cuda_backward_ + torch::zeros + gather_cuda_backward_
  * (cwarp_cuda_rnnt_kernel.cu:512-521, cwarp_cuda.cpp:131-135, cwarp_cuda_gather_kernel.cu:52-74) without mutating
@@ -250,6 +263,18 @@ CWRNNT_API int cwrnnt_validate(const cwrnnt_problem *p, const int32_t *lx, const
                                void *scratch, int32_t out[4], cwrnnt_stream_t stream);
 
 /*
+ * The same validation without the wait: the kernel and the 16-byte copy into HOST memory `out` are queued on `stream`
+ * and the call returns. The caller queues the loss kernels behind it (they protect themselves: invalid lengths make
+ * them return without touching the inputs, labels are clamped), and only then waits - on an event recorded right
+ * after this call, or on the stream - before reading `out` and raising. The GPU therefore never idles for the
+ * validation round trip, and the reference's host-side assertions (cwarp_rnnt/__init__.py:49,58) still fire before a
+ * loss is handed back. `out` should be pinned memory (a pageable buffer makes the copy synchronous) and, like
+ * `scratch`, must stay valid until the stream has passed this point. With B == 0 `out` is written at once.
+ */
+CWRNNT_API int cwrnnt_validate_async(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const int32_t *y,
+                                     void *scratch, int32_t out[4], cwrnnt_stream_t stream);
+
+/*
  * The joint network's broadcast-add written straight into the compact layout - the producer in front of the loss:
  *     out[off_n + t*(U_n+1) + u][:] = act(enc[n][t][:] + pred[n][u][:])
  * from the padded encoder output enc [B, t_max, H] and predictor output pred [B, u_max1, H] (p->dtype; H = p->V,
@@ -295,6 +320,13 @@ CWRNNT_API int cwrnnt_joint_backward(const cwrnnt_problem *p, int32_t activation
 #define CWRNNT_STATIC_MAX_SEQUENCES 1024
 CWRNNT_API int cwrnnt_costs_static(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly,
                                    const int32_t *y, void *costs, void *loss, cwrnnt_stream_t stream);
+/*
+ * Status words of the last cwrnnt_costs_static on the current device, as cwrnnt_read_status returns them for a
+ * caller-owned workspace (the built-in scratch cannot be handed to that function): 16 bytes copied to HOST memory
+ * `out`, one wait on `stream`, nothing allocated. Without it a clamped label (CWRNNT_ST_BAD_LABEL) would go unseen
+ * and invalid lengths would show only as NaN costs. No counterpart in the reference.
+ */
+CWRNNT_API int cwrnnt_static_status(int32_t out[4], cwrnnt_stream_t stream);
 
 /*
  * Host-buffer pipeline: logits, lengths and labels in HOST memory (pinned for overlap), costs / loss / gradients

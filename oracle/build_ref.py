@@ -12,9 +12,9 @@ with `-gencode arch=compute_100a,code=sm_100a` and writes only build products in
 The result, `oracle/_ref/cwarp_rnnt_ref_C.so`, exports the reference's three pybind functions
 (cwarp_cuda.cpp:138-153): `_cwarp_rnnt_forward`, `_cwarp_rnnt_backward`, `_cwarp_rnnt_loss`.
 It is used (a) to generate the golden fixtures under `tests/golden/` on a B200 and (b) as a live GPU
-comparator in the `-m gpu` tests and in `bench.py --ref-cuda` when the file is present.
+comparator in the `-m gpu` tests and in `bench.py --impl reference_cuda` when the file is present.
 
-Usage:  python oracle/build_ref.py [path-to-reference-tree]
+Usage:  python oracle/build_ref.py <path-to-reference-tree>      (or CWRNNT_REFERENCE_ROOT=<path> in the environment)
 """
 import os
 import sys
@@ -24,10 +24,17 @@ OUT = os.path.join(HERE, "_ref")
 NAME = "cwarp_rnnt_ref_C"
 
 
-DEFAULT_REFERENCE_ROOT = os.environ.get("CWRNNT_REFERENCE_ROOT", "/root/reference")
+def reference_root(arg=None):
+    """Where the reference tree is mounted: the argument, else CWRNNT_REFERENCE_ROOT. There is no built-in default."""
+    root = arg or os.environ.get("CWRNNT_REFERENCE_ROOT")
+    if not root:
+        raise FileNotFoundError("the reference tree's location is not known: pass it as the argument or set "
+                                "CWRNNT_REFERENCE_ROOT")
+    return root
 
 
-def build(ref_root: str = DEFAULT_REFERENCE_ROOT, verbose: bool = False) -> str:
+def build(ref_root=None, verbose: bool = False) -> str:
+    ref_root = reference_root(ref_root)
     srcs = [os.path.join(ref_root, f) for f in
             ("cwarp_cuda.cpp", "cwarp_cuda_gather_kernel.cu", "cwarp_cuda_rnnt_kernel.cu")]
     for s in srcs:

@@ -23,7 +23,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(L, n), n
     assert sorted(capi.EXPORTS) == names
-    assert L.cwrnnt_abi_version() == 2
+    assert L.cwrnnt_abi_version() == 3
 
 
 def test_descriptor_validation_and_workspace_size():

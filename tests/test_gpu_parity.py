@@ -247,26 +247,91 @@ def test_backward_is_repeatable_and_linear(oracle):
     assert g1.double().sum(-1).abs().max().item() < 1e-5
 
 
-@pytest.mark.parametrize("cfg", [1, 2, 5])
+@pytest.mark.parametrize("cfg", [1, 2, 3, 4, 5])
 def test_benchmark_shapes_properties(oracle, cfg):
-    """Full-size benchmark workloads (1: tiny; 2: Conformer V=1024 fp32, subset checked against the oracle;
-    5: ragged fp16): size-independent properties plus oracle parity on the sequences the oracle finishes quickly."""
+    """The five benchmark workloads exactly as `synth` generates them (1: tiny; 2: Conformer V=1024 fp32; 3: V=4096
+    bf16, reduction sum; 4: long-form, one 1000+ frame sequence; 5: ragged fp16): the leading sequences of each - as
+    many as the oracle finishes in seconds - against the oracle, plus the zero row sum of the logit gradient."""
     from compactwarprnntloss_b200 import synth
     from tests.gpu_helpers import run_engine
     lx, ly, y = synth.lengths_and_labels(cfg)
-    B = {1: 4, 2: 6, 5: 48}[cfg]
+    B = {1: 4, 2: 6, 3: 2, 4: 1, 5: 48}[cfg]
+    wl = synth.WORKLOADS[cfg]
     ids = list(range(B))
     x = synth.compact_logits(cfg, lx, ly, ids)
     case = dict(x=x.numpy() if x.dtype == torch.float32 else x, lx=lx[:B].numpy(), ly=ly[:B].numpy(),
                 y=y[:B].numpy(), blank=0, V=x.shape[1])
-    dtype = synth.WORKLOADS[cfg].dtype
-    got = run_engine(case, dtype=dtype, reduce="mean")
+    dtype = wl.dtype
+    got = run_engine(case, dtype=dtype, reduce=wl.reduction)
     xd = x.double().numpy()
-    costs, dense = oracle.fused(xd, case["lx"], case["ly"], case["y"], 0, weights=np.full(B, 1.0 / B))
+    w = np.full(B, 1.0 / B if wl.reduction == "mean" else 1.0)
+    costs, dense = oracle.fused(xd, case["lx"], case["ly"], case["y"], 0, weights=w)
+    assert got["status"][0] == 0
     np.testing.assert_allclose(got["costs"], costs, rtol=LOSS_RTOL)
-    atol = GRAD_ATOL + (2.0 ** -11 * np.abs(dense).max() if dtype == torch.float16 else 0.0)
-    assert np.abs(got["grad"] - dense).max() <= atol
-    assert np.abs(got["grad"].sum(-1)).max() < (1e-4 if dtype == torch.float32 else 2e-2)
+    want_loss = costs.mean() if wl.reduction == "mean" else costs.sum()
+    assert abs(got["loss"] - want_loss) <= LOSS_RTOL * abs(want_loss)
+    half_ulp = {torch.float32: 0.0, torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
+    assert np.abs(got["grad"] - dense).max() <= GRAD_ATOL + half_ulp * np.abs(dense).max()
+    row_sum = {torch.float32: 1e-4, torch.float16: 2e-2, torch.bfloat16: 5e-2}[dtype]
+    assert np.abs(got["grad"].sum(-1)).max() < row_sum
+
+
+def test_reference_test_generator_shape(oracle):
+    """The shape the reference's own test draws (test/test.py:10-25): fewer than 20 sequences, up to 511 frames, up to
+    512 labels, V = 3, the longest sequence reaching the padded sizes. Here with 12 sequences, T up to 300 and U up to
+    512, so that the 513-column lattice takes the single-role wavefront kernel while the 3-element rows take the
+    scalar (unaligned vocabulary) streaming kernels - the two paths no benchmark workload touches together."""
+    rng = np.random.default_rng(0)
+    N, T, U, V = 12, 300, 512, 3
+    lx = rng.integers(T // 2, T + 1, size=N).astype(np.int32)
+    ly = rng.integers(U // 2, U + 1, size=N).astype(np.int32)
+    lx += T - lx.max()
+    ly += U - ly.max()
+    y = rng.integers(1, V, size=(N, U)).astype(np.int32)
+    rows = int((lx.astype(np.int64) * (ly + 1)).sum())
+    case = dict(x=rng.standard_normal((rows, V)).astype(np.float32), lx=lx, ly=ly, y=y, blank=0, V=V)
+    _check_fused(oracle, case, reduce="mean")
+    # and as the reference is called: log-probabilities in, sparse gradient out
+    from tests.gpu_helpers import run_engine
+    lp = oracle.log_softmax(case["x"])
+    got = run_engine(dict(case, x=lp), fused=False)
+    g = oracle.gather(lp, lx, ly, y, 0)
+    fw = oracle.forward(g, lx, ly)
+    np.testing.assert_allclose(got["costs"], fw["costs"], rtol=LOSS_RTOL)
+    dense = oracle.backward(fw["grads"], np.ones(N), lx, ly, y, 0, V, accumulate_equal=True)
+    assert np.abs(got["grad"] - dense).max() <= GRAD_ATOL
+
+
+def test_forward_backward_guard(oracle):
+    """The reference's only consistency check (cwarp_cuda_rnnt_kernel.cu:350-366): alpha's and beta's log-likelihood of
+    a sequence more than 1e-3 apart (relative) -> their mean is the cost's log-likelihood and the status word gets
+    CWRNNT_ST_FWD_BWD_GAP. Driven through cwrnnt_fill_costs, which runs the same device function as the wavefront
+    kernel's epilogue, on hand-made log-likelihoods."""
+    from compactwarprnntloss_b200 import capi
+    dev = torch.device("cuda:0")
+    lx = torch.tensor([10, 20, 30, 40], dtype=torch.int32, device=dev)
+    la = torch.tensor([-100.0, -100.0, -50.0, -7.0], dtype=torch.float64, device=dev)
+    lb = torch.tensor([-100.05, -100.2, -50.0, -7.0000001], dtype=torch.float64, device=dev)
+    p = capi.Problem(0, 4, 4, 0, 0, 0, capi.F32, 0, 0)
+    costs = torch.zeros(4, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    capi.fill_costs(p, lx, la, lb, costs, status)
+    # |a-b|/|max| = 5e-4 (kept: beta), 2e-3 (mean), 0, 1.4e-8
+    np.testing.assert_allclose(costs.cpu().numpy(), [100.05, 100.1, 50.0, 7.0000001], rtol=2e-7)
+    assert int(status[0]) == capi.ST_FWD_BWD_GAP
+    status.zero_()
+    q = capi.Problem(0, 4, 2, 0, 0, 0, capi.F64, capi.AVERAGE_FRAMES, 0)
+    c64 = torch.zeros(2, dtype=torch.float64, device=dev)
+    capi.fill_costs(q, lx[2:], la[2:], lb[2:], c64, status)
+    np.testing.assert_allclose(c64.cpu().numpy(), [50.0 / 30, 7.0000001 / 40], rtol=1e-12)
+    assert int(status[0]) == 0
+    capi.fill_costs(q, lx[:2], None, lb[:2], c64, status)           # no alpha: no guard (costs-only path)
+    np.testing.assert_allclose(c64.cpu().numpy(), [100.05 / 10, 100.2 / 20], rtol=1e-12)
+    assert int(status[0]) == 0
+    # a real forward on a consistent lattice never raises the bit
+    from tests.gpu_helpers import run_engine
+    out = run_engine(ragged_case(3, 6, (5, 60), (1, 20), V=32), want_grad=False)
+    assert not out["status"][0] & capi.ST_FWD_BWD_GAP
 
 
 def test_sharded_forward_fills_global_cost_vector(oracle):

@@ -320,8 +320,9 @@ def test_many_tiny_sequences_in_groups(pipe):
 
 
 def test_invalid_lengths_stop_every_group(pipe):
-    """A row count that disagrees with the lengths is fatal: no group's kernels run, the costs are NaN, the status
-    says why, and the pipe is usable again afterwards."""
+    """A row count that disagrees with the lengths is fatal: no group's kernels do their work, the costs, the loss,
+    the cost vector and every element of the gradient are NaN, the status says why, and the pipe is usable again
+    afterwards."""
     case = ragged_case(6, 30, (10, 40), (2, 12), V=64)
     p, x, lx, ly, y = _setup(case)
     lx_bad = lx.clone()
@@ -330,11 +331,20 @@ def test_invalid_lengths_stop_every_group(pipe):
     costs = torch.zeros(p.B, device=DEV)
     loss = torch.zeros((), device=DEV)
     gx = torch.full_like(x, 5.0)
-    capi.loss_grad(p, x, lx_bad, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=4)
-    torch.cuda.synchronize()
-    st = capi.read_status(ws)
-    assert st[0] & capi.ST_ROW_MISMATCH
-    assert bool(torch.isnan(costs).all()) and bool((gx == 5.0).all())
+    vec = torch.zeros(p.B + 3, device=DEV)
+    for groups in (4, 1):
+        gx.fill_(5.0)
+        capi.loss_grad(p, x, lx_bad, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=groups, n_global=p.B + 2,
+                       cost_vector=vec)
+        torch.cuda.synchronize()
+        st = capi.read_status(ws)
+        assert st[0] & capi.ST_ROW_MISMATCH
+        assert bool(torch.isnan(costs).all()) and bool(torch.isnan(loss)) and bool(torch.isnan(vec).all())
+        assert bool(torch.isnan(gx).all())
+    gx.fill_(5.0)
+    capi.forward(p, x, lx_bad, ly, y, ws, costs, loss)
+    capi.backward(p, x, lx_bad, ly, y, ws, None, 0, gx)
+    assert bool(torch.isnan(loss)) and bool(torch.isnan(gx).all())
     c0, l0, g0 = _two_calls(p, x, lx, ly, y)
     c1, l1, g1, _ = _one_call(pipe, p, x, lx, ly, y, groups=4)
     _same(c0, c1)

@@ -82,3 +82,55 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert L.cwrnnt_costs_static(ctypes.byref(p), vp(x), vp(one), vp(one), vp(y), vp(costs), None, None) == capi.ERR_CAPACITY
     with pytest.raises(capi.CwrnntError, match="at most"):
         capi.costs_static(p, x, one, one, y, costs)
+
+
+def test_static_scratch_entry_point_at_its_stated_capacity(oracle):
+    """Exactly CWRNNT_STATIC_MAX_ROWS rows, and exactly CWRNNT_STATIC_MAX_SEQUENCES sequences: the carve of the
+    built-in array leaves a few KB of slack there, so the largest accepted problems are run for real against the
+    workspace entry point."""
+    from compactwarprnntloss_b200 import capi
+    rng = np.random.default_rng(77)
+    V = 8
+    # (a) the row limit with few, larger sequences: 128 lattices of 64 x 16 = 131072 rows
+    lx = np.full(128, 64, np.int32)
+    ly = np.full(128, 15, np.int32)
+    assert int((lx.astype(np.int64) * (ly + 1)).sum()) == capi.STATIC_MAX_ROWS
+    y = rng.integers(1, V, size=(128, 15)).astype(np.int32)
+    big_rows = dict(x=rng.standard_normal((capi.STATIC_MAX_ROWS, V)).astype(np.float32), lx=lx, ly=ly, y=y, blank=0, V=V)
+    # (b) the sequence limit: 1024 sequences of 128 rows -> also the row limit
+    lx = np.full(1024, 32, np.int32)
+    ly = np.full(1024, 3, np.int32)
+    y = rng.integers(1, V, size=(1024, 3)).astype(np.int32)
+    many = dict(x=rng.standard_normal((capi.STATIC_MAX_ROWS, V)).astype(np.float32), lx=lx, ly=ly, y=y, blank=0, V=V)
+    for case in (big_rows, many, big_rows):
+        want_c, want_l, got_c, got_l, _, _ = _both_ways(case, capi.FUSED_LOG_SOFTMAX | capi.REDUCE_SUM)
+        assert np.all(np.isfinite(got_c))
+        np.testing.assert_allclose(got_c, want_c, rtol=LOSS_RTOL, atol=1e-6)
+        assert abs(got_l - want_l) <= LOSS_RTOL * abs(want_l)
+        assert capi.static_status(torch.device("cuda:0"))[0] == 0
+    costs, _ = oracle.fused(many["x"], many["lx"], many["ly"], many["y"], 0, want_grad=False)
+    np.testing.assert_allclose(_both_ways(many, capi.FUSED_LOG_SOFTMAX)[2], costs, rtol=LOSS_RTOL, atol=1e-6)
+
+
+def test_static_scratch_entry_point_reports_its_status_words():
+    """The scratch is private, so the status of a call is read through cwrnnt_static_status: a clamped label and
+    lengths that do not add up must be visible there, not only as NaN costs."""
+    from compactwarprnntloss_b200 import capi
+    dev = torch.device("cuda:0")
+    case = ragged_case(903, 5, (3, 12), (1, 6), V=16)
+    x, lx, ly, y = _device_inputs(case)
+    p = capi.make_problem(x, lx, y, 0, capi.FUSED_LOG_SOFTMAX)
+    costs = torch.empty(p.B, device=dev)
+    capi.costs_static(p, x, lx, ly, y, costs)
+    assert capi.static_status(dev)[0] == 0
+    bad_y = y.clone()
+    bad_y[0, 0] = 16
+    capi.costs_static(p, x, lx, ly, bad_y, costs)
+    assert capi.static_status(dev)[0] == capi.ST_BAD_LABEL and bool(torch.isfinite(costs).all())
+    bad_lx = lx.clone()
+    bad_lx[2] += 1
+    capi.costs_static(p, x, bad_lx, ly, y, costs)
+    st = capi.static_status(dev)
+    assert st[0] & capi.ST_ROW_MISMATCH and bool(torch.isnan(costs).all())
+    capi.costs_static(p, x, lx, ly, y, costs)       # and the next good call starts from a clean header
+    assert capi.static_status(dev)[0] == 0 and bool(torch.isfinite(costs).all())
