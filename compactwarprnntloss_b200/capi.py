@@ -28,7 +28,7 @@ EXPORTS = [
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
     "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
-    "cwrnnt_pipe_wait_costs", "cwrnnt_validate", "cwrnnt_validate_async", "cwrnnt_static_status", "cwrnnt_fill_costs",
+    "cwrnnt_pipe_wait_costs", "cwrnnt_validate", "cwrnnt_validate_async", "cwrnnt_static_status", "cwrnnt_fill_costs", "cwrnnt_recursion",
 ]
 
 
@@ -81,6 +81,7 @@ def lib():
         L.cwrnnt_pack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_unpack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_costs_static.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
+        L.cwrnnt_recursion.argtypes = [pp, vp, vp, vp, i64, vp, vp, vp]
         L.cwrnnt_fill_costs.argtypes = [pp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_static_status.argtypes = [ctypes.POINTER(i32 * 4), vp]
         L.cwrnnt_read_status.argtypes = [vp, ctypes.POINTER(i32 * 4), vp]
@@ -154,6 +155,13 @@ def forward_sharded(p: Problem, x, lx, ly, y, workspace, costs, loss, global_ids
         check(lib().cwrnnt_forward_sharded(ctypes.byref(p), _ptr(x), _ptr(lx), _ptr(ly), _ptr(y), _ptr(workspace),
                                            workspace.numel(), _ptr(costs), _ptr(loss), _ptr(global_ids), n_global,
                                            _ptr(cost_vector), _stream(x.device)), "cwrnnt_forward_sharded")
+
+
+def recursion(p: Problem, lx, ly, workspace, costs, loss=None) -> None:
+    """The alpha/beta wavefront and the cost step alone, on a workspace a forward has already filled (same problem)."""
+    with torch.cuda.device(lx.device):
+        check(lib().cwrnnt_recursion(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(workspace), workspace.numel(),
+                                     _ptr(costs), _ptr(loss), _stream(lx.device)), "cwrnnt_recursion")
 
 
 def backward(p: Problem, x, lx, ly, y, workspace, grad_costs, grad_costs_stride, grad_x) -> None:

@@ -143,6 +143,20 @@ int cwrnnt_forward_sharded(const cwrnnt_problem *p, const void *x, const int32_t
     return forward_impl(p, x, lx, ly, y, workspace, workspace_bytes, costs, loss, &shard, stream);
 }
 
+int cwrnnt_recursion(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, void *workspace,
+                     int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    if (!lx || !ly || !costs) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, workspace_bytes, &w);
+    if (st) return st;
+    cudaError_t e = launch_wavefront(*p, lx, ly, w, costs, loss, nullptr, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("wavefront", e);
+}
+
 int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, const int32_t *ly, const int32_t *y,
                     const void *workspace, const void *grad_costs, int32_t grad_costs_stride, void *grad_x,
                     cwrnnt_stream_t stream)

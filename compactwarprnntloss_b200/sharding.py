@@ -12,27 +12,38 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 
-def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int) -> List[List[int]]:
+def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "longest_first") -> List[List[int]]:
     """Longest-processing-time-first assignment of sequences to ``world`` ranks.
 
     Weight of a sequence = its lattice size T*(U+1) (streaming cost is proportional to it for a fixed V); ties are
     broken by the wavefront critical path T+U, then by index, so every rank computes the same plan. Returns the global
-    sequence ids of each rank in ascending order (ascending keeps each rank's compact rows in global order).
+    sequence ids of each rank in the order the rank should lay its rows out in memory:
+
+    ``order="longest_first"`` (default)  descending T+U, ties by index. The pipelined step cuts a rank's rows into
+        groups in memory order and starts the alpha/beta wavefront of a group as soon as its rows are gathered; a
+        wavefront is a chain of T+U dependent steps, so the longest chains must start first to finish underneath the
+        streaming passes instead of after them. It is the sharding layer that decides a shard's row order, so this
+        costs nothing.
+    ``order="ascending"``  ascending global index (each rank's compact rows stay in global order).
     """
+    if order not in ("longest_first", "ascending"):
+        raise ValueError("order must be 'longest_first' or 'ascending'")
     if world < 1:
         raise ValueError("world must be >= 1")
     lx = [int(v) for v in lx]
     ly = [int(v) for v in ly]
     if len(lx) != len(ly):
         raise ValueError("lx and ly differ in length")
-    order = sorted(range(len(lx)), key=lambda i: (-(lx[i] * (ly[i] + 1)), -(lx[i] + ly[i]), i))
+    by_size = sorted(range(len(lx)), key=lambda i: (-(lx[i] * (ly[i] + 1)), -(lx[i] + ly[i]), i))
     load = [0] * world
     out: List[List[int]] = [[] for _ in range(world)]
-    for i in order:
+    for i in by_size:
         r = min(range(world), key=lambda k: (load[k], k))
         out[r].append(i)
         load[r] += lx[i] * (ly[i] + 1)
-    return [sorted(ids) for ids in out]
+    if order == "ascending":
+        return [sorted(ids) for ids in out]
+    return [sorted(ids, key=lambda i: (-(lx[i] + ly[i]), i)) for ids in out]
 
 
 def shard_imbalance(lx: Sequence[int], ly: Sequence[int], plan: List[List[int]]) -> float:

@@ -124,6 +124,17 @@ CWRNNT_API int cwrnnt_forward_sharded(const cwrnnt_problem *p, const void *x, co
                                       cwrnnt_stream_t stream);
 
 /*
+ * The alpha/beta recursion and the cost step by themselves, on a workspace that cwrnnt_forward (or cwrnnt_loss_grad)
+ * has already filled for the same problem and the same lx / ly: the gathered log-probabilities and the row offsets are
+ * taken as they stand, alpha, beta, costs and loss are recomputed. The counterpart of cwarp_cuda_costs_with_grad and,
+ * with CWRNNT_COSTS_ONLY, cwarp_cuda_cal_costs (cwarp_cuda_rnnt_kernel.cu:386-497, :523-576), which likewise start
+ * from gathered log-probabilities. Its duration divided by the longest T_n + U_n of the batch is the recursion's
+ * latency per lattice diagonal, the figure this stage is measured by.
+ */
+CWRNNT_API int cwrnnt_recursion(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, void *workspace,
+                                int64_t workspace_bytes, void *costs, void *loss, cwrnnt_stream_t stream);
+
+/*
  * Backward: grad_x[r][k] = d (sum_n g_n * costs[n]) / d x[r][k] in one streaming pass over [n_rows, V].
  * Replaces compact_rnnt_loss_backward_ (cwarp_cuda.cpp:110-136 = cwarp_cuda_backward_ + zeros[STU,V] +
  * gather_cuda_backward_) and, with CWRNNT_FUSED_LOG_SOFTMAX, the caller's log_softmax backward as well.

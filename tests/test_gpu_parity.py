@@ -163,6 +163,27 @@ def test_costs_only_matches_full(oracle):
     np.testing.assert_allclose(only["costs"], costs, rtol=LOSS_RTOL)
 
 
+def test_recursion_alone_on_a_gathered_workspace(oracle):
+    """cwrnnt_recursion re-runs the alpha/beta wavefront and the cost step on the state a forward left behind: costs
+    and loss come out bit-identical, with and without the alpha direction, and a backward may still follow."""
+    from compactwarprnntloss_b200 import capi
+    from tests.gpu_helpers import run_engine
+    case = ragged_case(14, 9, (3, 70), (0, 40), V=24)
+    out = run_engine(case, reduce="mean", keep=True)
+    p, ws = out["p"], out["ws"]
+    costs = torch.full((p.B,), float("nan"), device="cuda:0")
+    loss = torch.full((), float("nan"), device="cuda:0")
+    capi.recursion(p, out["lx"], out["ly"], ws, costs, loss)
+    assert np.array_equal(costs.double().cpu().numpy(), out["costs"]) and float(loss) == out["loss"]
+    gx = torch.empty_like(out["x"])
+    capi.backward(p, out["x"], out["lx"], out["ly"], out["y"], ws, None, 0, gx)
+    assert np.array_equal(gx.double().cpu().numpy(), out["grad"])
+    q = capi.make_problem(out["x"], out["lx"], out["y"], 0, capi.FUSED_LOG_SOFTMAX | capi.COSTS_ONLY)
+    costs.fill_(float("nan"))
+    capi.recursion(q, out["lx"], out["ly"], ws, costs, None)       # beta only
+    np.testing.assert_allclose(costs.double().cpu().numpy(), out["costs"], rtol=1e-6)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float64])
 def test_log_prob_mode_is_reference_contract(oracle, dtype):
     """x = log-probs: costs, sparse dense-shaped gradient, pair gradients and padded alpha/beta as the reference."""

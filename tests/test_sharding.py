@@ -17,7 +17,11 @@ def test_plan_is_balanced_deterministic_and_complete():
         plan = sharding.plan_shards(lx.tolist(), ly.tolist(), world)
         sharding.validate_plan(plan, len(lx))
         assert plan == sharding.plan_shards(lx.tolist(), ly.tolist(), world)
-        assert all(ids == sorted(ids) for ids in plan)
+        # default row order of a shard: longest critical path (T+U) first, so its wavefront starts first
+        chain = (lx + ly).tolist()
+        assert all(all(chain[a] >= chain[b] for a, b in zip(ids, ids[1:])) for ids in plan)
+        asc = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order="ascending")
+        assert [sorted(ids) for ids in plan] == asc and all(ids == sorted(ids) for ids in asc)
         assert sharding.shard_imbalance(lx, ly, plan) < 1.05
     lx2, ly2, _ = synth.lengths_and_labels(2, B=64)
     assert sharding.shard_imbalance(lx2, ly2, sharding.plan_shards(lx2, ly2, 8)) < 1.05
@@ -28,6 +32,8 @@ def test_plan_rejects_bad_input_and_bad_plans():
         sharding.plan_shards([1, 2], [1], 2)
     with pytest.raises(ValueError):
         sharding.plan_shards([1], [1], 0)
+    with pytest.raises(ValueError):
+        sharding.plan_shards([1], [1], 1, order="random")
     with pytest.raises(ValueError):
         sharding.validate_plan([[0, 1], [1, 2]], 3)   # sequence 1 twice: ranks disagree on the plan
     with pytest.raises(ValueError):
