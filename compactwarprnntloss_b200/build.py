@@ -20,7 +20,7 @@ OBJ = os.path.join(PKG, "build")
 LIB = os.path.join(PKG, "libcwarp_rnnt_b200.so")
 
 CU_SOURCES = ["cwrnnt_prep.cu", "cwrnnt_gather.cu", "cwrnnt_wavefront.cu", "cwrnnt_grad.cu", "cwrnnt_compat.cu",
-              "cwrnnt_pack.cu", "cwrnnt_joint.cu", "cwrnnt_api.cu", "cwrnnt_host.cu", "cwrnnt_static.cu"]
+              "cwrnnt_pack.cu", "cwrnnt_joint.cu", "cwrnnt_align.cu", "cwrnnt_api.cu", "cwrnnt_host.cu", "cwrnnt_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-I", INC, "-I", CSRC]
 

@@ -28,7 +28,8 @@ EXPORTS = [
     "cwrnnt_host_ctx_error", "cwrnnt_loss_grad_host", "cwrnnt_costs_static", "cwrnnt_forward_sharded",
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
     "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
-    "cwrnnt_pipe_wait_costs", "cwrnnt_validate", "cwrnnt_validate_async", "cwrnnt_static_status", "cwrnnt_fill_costs", "cwrnnt_recursion",
+    "cwrnnt_pipe_wait_costs", "cwrnnt_validate", "cwrnnt_validate_async", "cwrnnt_static_status", "cwrnnt_fill_costs", "cwrnnt_recursion", "cwrnnt_alignment_scratch_bytes", "cwrnnt_export_alignment",
+    "cwrnnt_export_posteriors",
 ]
 
 
@@ -81,6 +82,10 @@ def lib():
         L.cwrnnt_pack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_unpack_padded.argtypes = [pp, vp, i32, i32, vp, vp, vp, i64, vp, vp]
         L.cwrnnt_costs_static.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp]
+        L.cwrnnt_alignment_scratch_bytes.restype = i64
+        L.cwrnnt_alignment_scratch_bytes.argtypes = [pp]
+        L.cwrnnt_export_alignment.argtypes = [pp, vp, vp, vp, vp, i64, i32, vp, vp, vp]
+        L.cwrnnt_export_posteriors.argtypes = [pp, vp, vp, vp, i32, i32, vp, vp]
         L.cwrnnt_recursion.argtypes = [pp, vp, vp, vp, i64, vp, vp, vp]
         L.cwrnnt_fill_costs.argtypes = [pp, vp, vp, vp, vp, vp, vp]
         L.cwrnnt_static_status.argtypes = [ctypes.POINTER(i32 * 4), vp]
@@ -235,6 +240,31 @@ def export_alpha_beta(p: Problem, lx, ly, workspace, t_max, u_max1, alphas, beta
         check(lib().cwrnnt_export_alpha_beta(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(workspace), t_max, u_max1,
                                              _ptr(alphas), _ptr(betas), _stream(lx.device)),
               "cwrnnt_export_alpha_beta")
+
+
+def export_alignment(p: Problem, lx, ly, workspace, path_stride: int):
+    """Best path of every sequence from a forward's workspace: (moves [B, path_stride] int32 - 0 blank move, 1 label
+    move, -1 padding - and scores [B], the paths' log-probabilities)."""
+    dev = lx.device
+    n = lib().cwrnnt_alignment_scratch_bytes(ctypes.byref(p))
+    scratch = torch.empty(n, dtype=torch.uint8, device=dev)
+    moves = torch.empty(p.B, path_stride, dtype=torch.int32, device=dev)
+    scores = torch.empty(p.B, dtype=torch.float64 if p.dtype == F64 else torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().cwrnnt_export_alignment(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(workspace), _ptr(scratch), n,
+                                            path_stride, _ptr(moves), _ptr(scores), _stream(dev)),
+              "cwrnnt_export_alignment")
+    return moves, scores
+
+
+def export_posteriors(p: Problem, lx, ly, workspace, t_max: int, u_max1: int):
+    """Node posteriors exp(alpha + beta - log P) as a zero-padded [B, t_max, u_max1] tensor of the costs dtype."""
+    dev = lx.device
+    post = torch.empty(p.B, t_max, u_max1, dtype=torch.float64 if p.dtype == F64 else torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib().cwrnnt_export_posteriors(ctypes.byref(p), _ptr(lx), _ptr(ly), _ptr(workspace), t_max, u_max1,
+                                             _ptr(post), _stream(dev)), "cwrnnt_export_posteriors")
+    return post
 
 
 def scatter_backward(p: Problem, grads, grad_costs, lx, ly, y, dense) -> None:

@@ -14,8 +14,11 @@ struct cwrnnt_pipe {
     int device;
     cudaStream_t alt;                  // streaming kernels of the odd groups (even ones: the caller's stream)
     cudaStream_t side[kMaxGroups];     // highest priority: the wavefront of group g
+    cudaStream_t grad[kMaxGroups];     // the gradient of group g: one stream per group, so that the groups' gradient
+                                       // launches start in the order in which their wavefronts FINISH
     cudaEvent_t gathered[kMaxGroups];  // recorded after the gather of range g
     cudaEvent_t solved[kMaxGroups];    // recorded on side[g] after the wavefront of group g
+    cudaEvent_t graded[kMaxGroups];    // recorded on grad[g] after the gradient of group g
     cudaEvent_t forked, joined;        // caller's stream -> alt at the start, alt -> caller's stream at the end
     cudaEvent_t costs_ready;           // every wavefront of the last step is done: costs, loss, cost vector written
 };
@@ -192,8 +195,10 @@ int cwrnnt_pipe_create(cwrnnt_pipe **out)
     for (int g = 0; g < kMaxGroups && e == cudaSuccess; ++g) {
         // highest priority: a wavefront CTA must get onto an SM as soon as a CTA of the streaming kernels retires
         e = cudaStreamCreateWithPriority(&pipe->side[g], cudaStreamNonBlocking, greatest);
+        if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&pipe->grad[g], cudaStreamNonBlocking, least);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->gathered[g], cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->solved[g], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->graded[g], cudaEventDisableTiming);
     }
     if (e != cudaSuccess) {
         fail_launch("pipe_create", e);
@@ -213,8 +218,10 @@ void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe)
     if (pipe->costs_ready) cudaEventDestroy(pipe->costs_ready);
     for (int g = 0; g < kMaxGroups; ++g) {
         if (pipe->side[g]) cudaStreamDestroy(pipe->side[g]);
+        if (pipe->grad[g]) cudaStreamDestroy(pipe->grad[g]);
         if (pipe->gathered[g]) cudaEventDestroy(pipe->gathered[g]);
         if (pipe->solved[g]) cudaEventDestroy(pipe->solved[g]);
+        if (pipe->graded[g]) cudaEventDestroy(pipe->graded[g]);
     }
     delete pipe;
 }
@@ -282,22 +289,34 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
         for (int g = 1; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(collect, pipe->solved[g], 0), "event");
         CWRNNT_TRY(cudaEventRecord(pipe->costs_ready, collect), "event");
     }
+    // The gradient of group g runs on its own stream behind `solved[g]` alone, so the groups' gradient launches start
+    // in the order in which their wavefronts finish, whatever the order of the rows: a group of short lattices that
+    // was gathered last is differentiated while the long chains of an earlier group are still running. Launches that
+    // are ready together are dispatched in issue order (group 0 first), each filling in as the one before runs out of
+    // CTAs, exactly as two alternating streams would.
     for (int g = 0; g < G; ++g) {
         GradRows span{nullptr, 0, 0, 0};
+        cudaStream_t k3 = s;
         if (G > 1) {
-            CWRNNT_TRY(cudaStreamWaitEvent(rows_stream(g), pipe->solved[g], 0), "event");
+            k3 = pipe->grad[g];
+            CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->solved[g], 0), "event");
+            // the gathers that share rows with this group precede solved[g]; grad_x must also not be written before
+            // the caller's earlier work on `stream` is done
+            CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->forked, 0), "event");
             // a group holds the sequences that END in its range, so it is about one range long, give or take a
             // sequence: the grid is sized for one range and a longer group is finished by the same CTAs
             const int64_t row0 = g * plan.range_rows;
             span = GradRows{w.bounds + g, plan.range_rows, row0, g == G - 1 ? p->n_rows : row0 + plan.range_rows};
         }
-        CWRNNT_TRY(launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x, rows_stream(g), span),
-                   "grad");
+        CWRNNT_TRY(launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x, k3, span), "grad");
+        if (G > 1) CWRNNT_TRY(cudaEventRecord(pipe->graded[g], k3), "event");
     }
     if (G > 1) {
-        // join: everything issued on alt, and the collecting side stream (every wavefront stream is behind it)
+        // join: the gathers issued on alt, every gradient stream, and the collecting side stream (every wavefront
+        // stream is behind it)
         CWRNNT_TRY(cudaEventRecord(pipe->joined, pipe->alt), "event");
         CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->joined, 0), "event");
+        for (int g = 0; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->graded[g], 0), "event");
         CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->costs_ready, 0), "event");
     }
 #undef CWRNNT_TRY
@@ -356,6 +375,44 @@ int cwrnnt_export_alpha_beta(const cwrnnt_problem *p, const int32_t *lx, const i
     cudaError_t e = launch_export_ab(*p, lx, ly, w, t_max, u_max1, alphas, betas,
                                      reinterpret_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? CWRNNT_OK : fail_launch("export_alpha_beta", e);
+}
+
+int64_t cwrnnt_alignment_scratch_bytes(const cwrnnt_problem *p)
+{
+    if (check_problem(p) != CWRNNT_OK) return -1;
+    return align_up(p->n_rows > 0 ? p->n_rows : 1, 256);
+}
+
+int cwrnnt_export_alignment(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const void *workspace,
+                            void *scratch, int64_t scratch_bytes, int32_t path_stride, int32_t *moves, void *scores,
+                            cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if (p->B == 0) return CWRNNT_OK;
+    if (!lx || !ly || !moves || !scores || path_stride < 1) return CWRNNT_ERR_ARGUMENT;
+    if (!scratch || scratch_bytes < cwrnnt_alignment_scratch_bytes(p)) return CWRNNT_ERR_WORKSPACE;
+    Workspace w{};
+    st = check_workspace(p, workspace, -1, &w);
+    if (st) return st;
+    cudaError_t e = launch_alignment(*p, lx, ly, w, static_cast<unsigned char *>(scratch), path_stride, moves, scores,
+                                     reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("export_alignment", e);
+}
+
+int cwrnnt_export_posteriors(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly, const void *workspace,
+                             int32_t t_max, int32_t u_max1, void *posteriors, cwrnnt_stream_t stream)
+{
+    int st = check_problem(p);
+    if (st) return st;
+    if ((p->flags & CWRNNT_COSTS_ONLY) || !lx || !ly || t_max < 0 || u_max1 < 0) return CWRNNT_ERR_ARGUMENT;
+    Workspace w{};
+    st = check_workspace(p, workspace, -1, &w);
+    if (st) return st;
+    if (p->B == 0 || int64_t(t_max) * u_max1 == 0) return CWRNNT_OK;
+    if (!posteriors) return CWRNNT_ERR_ARGUMENT;
+    cudaError_t e = launch_posteriors(*p, lx, ly, w, t_max, u_max1, posteriors, reinterpret_cast<cudaStream_t>(stream));
+    return e == cudaSuccess ? CWRNNT_OK : fail_launch("export_posteriors", e);
 }
 
 int cwrnnt_fill_costs(const cwrnnt_problem *p, const int32_t *lx, const double *ll_alpha, const double *ll_beta,

@@ -61,6 +61,13 @@ cudaError_t launch_export_ab(const cwrnnt_problem &p, const int32_t *lx, const i
 cudaError_t launch_scatter(const cwrnnt_problem &p, const void *grads, const void *grad_costs, const int32_t *lx,
                            const int32_t *ly, const int32_t *y, int64_t *off_scratch, void *dense, cudaStream_t s);
 
+// Analysis exports: best path of every sequence (`back`: one byte per lattice node of scratch) and node posteriors in
+// the padded [B, t_max, u_max1] layout.
+cudaError_t launch_alignment(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
+                             unsigned char *back, int32_t stride, int32_t *moves, void *scores, cudaStream_t s);
+cudaError_t launch_posteriors(const cwrnnt_problem &p, const int32_t *lx, const int32_t *ly, const Workspace &w,
+                              int32_t t_max, int32_t u_max1, void *post, cudaStream_t s);
+
 // Costs from per-sequence log-likelihoods with the forward/backward guard (ll_alpha may be null: no guard).
 cudaError_t launch_fill_costs(const cwrnnt_problem &p, const int32_t *lx, const double *ll_alpha,
                               const double *ll_beta, void *costs, int32_t *status, cudaStream_t s);

@@ -214,6 +214,27 @@ CWRNNT_API int cwrnnt_export_alpha_beta(const cwrnnt_problem *p, const int32_t *
                              int32_t t_max, int32_t u_max1, void *alphas, void *betas, cwrnnt_stream_t stream);
 
 /*
+ * What the reference leaves to the caller of its alpha / beta outputs (cwarp_cuda_rnnt_kernel.cu:383-384 "for
+ * debugging or analysis", returned at :496), computed from the state cwrnnt_forward left in the workspace:
+ * cwrnnt_export_alignment: the most probable alignment of every sequence - the alpha recursion (:105-125) with max in
+ *   place of log-sum-exp, then a walk back from (T-1,U). moves [B, path_stride] int32: moves[n][k], k < T_n+U_n, is 0
+ *   for a blank move (next frame) and 1 for a label move (next label), the last one being the final blank; -1 beyond
+ *   (path_stride >= max_n T_n+U_n, shorter rows are truncated at the front). Equal scores go to the blank move.
+ *   scores [B] (costs type): log-probability of that path. scratch: cwrnnt_alignment_scratch_bytes(p) bytes (one per
+ *   lattice node). Works after a CWRNNT_COSTS_ONLY forward too (it reads the gathered log-probabilities only).
+ * cwrnnt_export_posteriors: exp(alpha(t,u) + beta(t,u) - log P(y|x)), the probability that the alignment passes
+ *   through node (t,u), zero-padded [B, t_max, u_max1] of the costs type like the alpha / beta export; the entries of
+ *   every anti-diagonal t+u = d of a sequence add up to one.
+ */
+CWRNNT_API int64_t cwrnnt_alignment_scratch_bytes(const cwrnnt_problem *p);
+CWRNNT_API int cwrnnt_export_alignment(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly,
+                                       const void *workspace, void *scratch, int64_t scratch_bytes,
+                                       int32_t path_stride, int32_t *moves, void *scores, cwrnnt_stream_t stream);
+CWRNNT_API int cwrnnt_export_posteriors(const cwrnnt_problem *p, const int32_t *lx, const int32_t *ly,
+                                        const void *workspace, int32_t t_max, int32_t u_max1, void *posteriors,
+                                        cwrnnt_stream_t stream);
+
+/*
  * The cost step by itself: costs[n] = -ll[n] (divided by T_n under CWRNNT_AVERAGE_FRAMES) from per-sequence
  * log-likelihoods held in DEVICE double arrays - ll_alpha[n] = alpha(T-1,U) + the final blank, ll_beta[n] = beta(0,0).
  * Replaces fill_cost_kernel (cwarp_cuda_rnnt_kernel.cu:334-367) including its consistency guard: where the two differ

@@ -163,7 +163,58 @@ def fused_f32io(x, lx, ly, y, blank, weights=None, want_grad=True, dense_out=Non
     return costs, dense
 
 
+def viterbi(g, lx, ly):
+    """Best path of every sequence from gathered log-probs [STU,2] in double. Returns (moves [N, max(T+U)] int32 -
+    0 = blank move, 1 = label move, -1 beyond T_n+U_n - and the paths' log-probabilities [N])."""
+    g, lx, ly = _c(g, np.float64), _c(lx, np.int32), _c(ly, np.int32)
+    off, rows = offsets(lx, ly)
+    assert rows == g.shape[0]
+    N = len(lx)
+    stride = int((lx.astype(np.int64) + ly).max()) if N else 0
+    moves = np.zeros((N, stride), dtype=np.int32)
+    scores = np.zeros(N)
+    lib().oracle_viterbi_f64(_p(g, _f64p), _p(lx, _i32p), _p(ly, _i32p), ctypes.c_int64(N), _p(off, _i64p),
+                             ctypes.c_int64(stride), _p(moves, _i32p), _p(scores, _f64p))
+    return moves, scores
+
+
+def posteriors(g, lx, ly):
+    """exp(alpha + beta - log P) of every lattice node, compact [STU] in (t,u) row-major order per sequence."""
+    g, lx, ly = _c(g, np.float64), _c(lx, np.int32), _c(ly, np.int32)
+    off, rows = offsets(lx, ly)
+    assert rows == g.shape[0]
+    post = np.zeros(rows)
+    lib().oracle_posteriors_f64(_p(g, _f64p), _p(lx, _i32p), _p(ly, _i32p), ctypes.c_int64(len(lx)), _p(off, _i64p),
+                                _p(post, _f64p))
+    return post
+
+
 # ---------------------------------------------------------------- independent brute force (tiny lattices only)
+
+def brute_force_best_path(lp_blank, lp_label):
+    """(log-probability, moves) of the most probable monotone path through a T x (U+1) lattice, by enumeration; moves
+    as in `viterbi` (the final blank included). Ties: the path whose label moves come latest, which is what a
+    recursion that prefers the blank move on equal scores walks back to... only when no tie occurs is the path
+    unique, so callers compare scores, and paths only on inputs without ties (random reals)."""
+    T, m = len(lp_blank), len(lp_blank[0])
+    U = m - 1
+    best, best_moves = -math.inf, None
+    for labels_at in itertools.combinations(range(T - 1 + U), U):
+        t = u = 0
+        logp = 0.0
+        pos = set(labels_at)
+        for step in range(T - 1 + U):
+            if step in pos:
+                logp += lp_label[t][u]
+                u += 1
+            else:
+                logp += lp_blank[t][u]
+                t += 1
+        logp += lp_blank[T - 1][U]
+        if logp > best:
+            best, best_moves = logp, [1 if k in pos else 0 for k in range(T - 1 + U)] + [0]
+    return best, best_moves
+
 
 def brute_force_cost(lp_blank, lp_label):
     """-log of the summed probability of every monotone path through a T x (U+1) lattice.

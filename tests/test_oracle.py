@@ -158,3 +158,54 @@ def test_property_random_tiny_lattices_match_brute_force(oracle):
         assert abs(costs[0] - want) < 1e-9 and np.abs(dense.sum(-1)).max() < 1e-12
 
     run()
+
+
+@pytest.mark.parametrize("T,U", [(1, 0), (1, 3), (4, 0), (2, 2), (4, 3), (5, 4), (3, 6)])
+def test_best_path_matches_enumeration(oracle, T, U):
+    """The max-product recursion and its walk back against the most probable of all enumerated monotone paths."""
+    c = ragged_case(300 + 10 * T + U, 1, (T, T), (U, U), V=5)
+    g = oracle.gather(oracle.log_softmax(c["x"]), c["lx"], c["ly"], c["y"], 0)
+    moves, scores = oracle.viterbi(g, c["lx"], c["ly"])
+    want, want_moves = oracle.brute_force_best_path(g[:, 0].reshape(T, U + 1).tolist(),
+                                                    g[:, 1].reshape(T, U + 1).tolist())
+    assert abs(scores[0] - want) < 1e-12
+    assert moves.shape == (1, T + U) and moves[0].tolist() == want_moves      # random reals: no ties
+    assert moves[0, -1] == 0 and int(moves[0].sum()) == U
+    # the best path is one of the summed paths: its probability cannot exceed the total
+    assert scores[0] <= -oracle.costs_only(g, c["lx"], c["ly"])[0] + 1e-12
+
+
+def test_best_paths_of_a_ragged_batch_are_padded_and_consistent(oracle):
+    c = ragged_case(41, 6, (1, 30), (0, 12), V=9)
+    g = oracle.gather(oracle.log_softmax(c["x"]), c["lx"], c["ly"], c["y"], 0)
+    moves, scores = oracle.viterbi(g, c["lx"], c["ly"])
+    off, _ = oracle.offsets(c["lx"], c["ly"])
+    for n in range(6):
+        T, U = int(c["lx"][n]), int(c["ly"][n])
+        mv = moves[n]
+        assert np.all(mv[T + U:] == -1) and set(mv[:T + U].tolist()) <= {0, 1}
+        assert int(mv[:T + U].sum()) == U
+        # re-score the path from the gathered log-probs
+        t = u = 0
+        total = 0.0
+        for k in mv[:T + U]:
+            r = off[n] + t * (U + 1) + u
+            total += g[r, int(k)]
+            t, u = (t, u + 1) if k else (t + 1, u)
+        assert (t, u) == (T, U) and abs(total - scores[n]) < 1e-10
+
+
+def test_node_posteriors_sum_to_one_on_every_diagonal(oracle):
+    """Every alignment crosses each anti-diagonal t+u = d exactly once, so the node posteriors of a diagonal add up to
+    one; the corner cells have posterior one."""
+    c = ragged_case(43, 4, (2, 25), (0, 10), V=7)
+    g = oracle.gather(oracle.log_softmax(c["x"]), c["lx"], c["ly"], c["y"], 0)
+    post = oracle.posteriors(g, c["lx"], c["ly"])
+    off, _ = oracle.offsets(c["lx"], c["ly"])
+    for n in range(4):
+        T, m = int(c["lx"][n]), int(c["ly"][n]) + 1
+        p = post[off[n]:off[n] + T * m].reshape(T, m)
+        assert abs(p[0, 0] - 1) < 1e-12 and abs(p[-1, -1] - 1) < 1e-12
+        for d in range(T + m - 1):
+            s = sum(p[t, d - t] for t in range(T) if 0 <= d - t < m)
+            assert abs(s - 1) < 1e-10
