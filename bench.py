@@ -66,7 +66,7 @@ def parse():
                     help="weak: B*N sequences over N GPUs (default); strong: the workload's B sequences sharded over N")
     ap.add_argument("--groups", type=int, default=0,
                     help="sequence groups of the pipelined step (0 = chosen by the library, 1 = no overlap)")
-    ap.add_argument("--order", default="longest_first", choices=["longest_first", "ascending"],
+    ap.add_argument("--order", default="longest_first", choices=["longest_first", "pipeline", "ascending"],
                     help="row order of a rank's sequences (sharding.plan_shards)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -348,6 +348,7 @@ class Job:
         self.ids_dev = torch.tensor(ids, dtype=torch.int32, device=dev)
         self.pipe = capi.Pipe(dev)
         self.n_groups = capi.pipeline_groups(self.p, groups)
+        self.launches = 1 + 3 * self.n_groups
         self.nodes = x.shape[0]
         self.elt = x.element_size()
         self.longest = max((int(lx[i]) + int(ly[i]) for i in ids), default=0)
@@ -468,6 +469,7 @@ def config_block(job, m, K, peak, peak_kind):
     step_gbs = 3.0 * job.nodes * wl.V * job.elt / (ms * 1e-3) / 1e9
     out = {"workload": wl.name, "dtype": DTYPE_NAME[wl.dtype], "lattice_nodes": job.nodes,
            "logits_bytes": int(job.nodes * wl.V * job.elt), "sequence_groups": job.n_groups,
+           "gpu_launches_per_step": job.launches,
            "ms_per_step": ms, "ms_per_step_min": sp["min"], "ms_per_step_max": sp["max"], "steps": K,
            "blocks": sp["blocks"], "value": job.nodes / (ms * 1e-3), "unit": UNIT,
            "step_roofline": {"achieved": step_gbs, "peak": peak, "unit": "GB/s", "frac": step_gbs / peak,
@@ -715,8 +717,8 @@ def main():
                    "timed_region_ms": sum(blocks),
                    "what": "each block: barrier + synchronize, CUDA event, K steps, CUDA event, barrier + synchronize; "
                            "max over ranks per block; ms_per_step and value are the median block"},
-        "gpu_launches": (1 + 3 * n_groups) * K * repeats,
-        "gpu_launches_per_step": 1 + 3 * n_groups,
+        "gpu_launches": job.launches * K * repeats,
+        "gpu_launches_per_step": job.launches,
         "kernels_per_step": ["prep_kernel"] + ["gather_rows_kernel", "wavefront_split_kernel",
                                                "grad_rows_kernel"] * n_groups,
         "pipeline": {"entry": "cwrnnt_loss_grad", "sequence_groups": n_groups,

@@ -29,7 +29,7 @@ EXPORTS = [
     "cwrnnt_pack_padded", "cwrnnt_unpack_padded", "cwrnnt_pipe_create", "cwrnnt_pipe_destroy", "cwrnnt_loss_grad",
     "cwrnnt_scale_grad", "cwrnnt_pipeline_groups", "cwrnnt_joint_forward", "cwrnnt_joint_backward",
     "cwrnnt_pipe_wait_costs", "cwrnnt_validate", "cwrnnt_validate_async", "cwrnnt_static_status", "cwrnnt_fill_costs", "cwrnnt_recursion", "cwrnnt_alignment_scratch_bytes", "cwrnnt_export_alignment",
-    "cwrnnt_export_posteriors",
+    "cwrnnt_export_posteriors", "cwrnnt_pipe_create_traced", "cwrnnt_pipe_timeline",
 ]
 
 
@@ -65,6 +65,8 @@ def lib():
         L.cwrnnt_forward_sharded.argtypes = [pp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, vp, vp]
         L.cwrnnt_backward.argtypes = [pp, vp, vp, vp, vp, vp, vp, i32, vp, vp]
         L.cwrnnt_pipe_create.argtypes = [ctypes.POINTER(vp)]
+        L.cwrnnt_pipe_create_traced.argtypes = [ctypes.POINTER(vp)]
+        L.cwrnnt_pipe_timeline.argtypes = [vp, ctypes.POINTER(ctypes.c_float), i32]
         L.cwrnnt_pipe_destroy.argtypes = [vp]
         L.cwrnnt_pipe_destroy.restype = None
         L.cwrnnt_pipe_wait_costs.argtypes = [vp, vp]
@@ -179,12 +181,22 @@ def backward(p: Problem, x, lx, ly, y, workspace, grad_costs, grad_costs_stride,
 class Pipe:
     """Side streams and events of the pipelined step (cwrnnt_pipe_create); bound to one device, one call at a time."""
 
-    def __init__(self, device):
+    def __init__(self, device, traced: bool = False):
         self.device = torch.device("cuda", device) if not isinstance(device, torch.device) else device
         self._h = ctypes.c_void_p()
         with torch.cuda.device(self.device):
             torch.cuda.current_stream()  # make sure the primary context exists
-            check(lib().cwrnnt_pipe_create(ctypes.byref(self._h)), "cwrnnt_pipe_create")
+            make = lib().cwrnnt_pipe_create_traced if traced else lib().cwrnnt_pipe_create
+            check(make(ctypes.byref(self._h)), "cwrnnt_pipe_create")
+
+    def timeline(self):
+        """Per sequence group of the last step (traced pipes, after a synchronise): [ms since the fork point at which
+        its range was gathered, its wavefront was done, its gradient was done]."""
+        buf = (ctypes.c_float * 24)()
+        n = lib().cwrnnt_pipe_timeline(self._h, buf, 24)
+        if n < 0:
+            raise CwrnntError("cwrnnt_pipe_timeline: the pipe is not traced")
+        return [[buf[3 * g + k] for k in range(3)] for g in range(n)]
 
     def wait_costs(self, stream: torch.cuda.Stream) -> None:
         """`stream` waits until the costs / loss / cost vector of the last loss_grad on this pipe are written (its

@@ -13,14 +13,14 @@ using namespace cwrnnt;
 struct cwrnnt_pipe {
     int device;
     cudaStream_t alt;                  // streaming kernels of the odd groups (even ones: the caller's stream)
-    cudaStream_t side[kMaxGroups];     // highest priority: the wavefront of group g
-    cudaStream_t grad[kMaxGroups];     // the gradient of group g: one stream per group, so that the groups' gradient
-                                       // launches start in the order in which their wavefronts FINISH
+    cudaStream_t side[kMaxGroups];     // highest priority: the wavefront of group g, then its gradient
     cudaEvent_t gathered[kMaxGroups];  // recorded after the gather of range g
     cudaEvent_t solved[kMaxGroups];    // recorded on side[g] after the wavefront of group g
-    cudaEvent_t graded[kMaxGroups];    // recorded on grad[g] after the gradient of group g
+    cudaEvent_t graded[kMaxGroups];    // recorded on side[g] after the gradient of group g
     cudaEvent_t forked, joined;        // caller's stream -> alt at the start, alt -> caller's stream at the end
     cudaEvent_t costs_ready;           // every wavefront of the last step is done: costs, loss, cost vector written
+    bool traced;                       // events carry timestamps (cwrnnt_pipe_create_traced): cwrnnt_pipe_timeline works
+    int last_groups;                   // group count of the last step issued through this pipe
 };
 
 namespace {
@@ -179,26 +179,27 @@ int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int32_t *lx, c
     return e == cudaSuccess ? CWRNNT_OK : fail_launch("grad", e);
 }
 
-int cwrnnt_pipe_create(cwrnnt_pipe **out)
+static int pipe_create(cwrnnt_pipe **out, bool traced)
 {
     if (!out) return CWRNNT_ERR_ARGUMENT;
     *out = nullptr;
     cwrnnt_pipe *pipe = new (std::nothrow) cwrnnt_pipe{};
     if (!pipe) return CWRNNT_ERR_LAUNCH;
+    pipe->traced = traced;
+    const unsigned ev_flags = traced ? cudaEventDefault : cudaEventDisableTiming;  // timestamps only when traced
     int least = 0, greatest = 0;
     cudaError_t e = cudaGetDevice(&pipe->device);
     if (e == cudaSuccess) e = cudaDeviceGetStreamPriorityRange(&least, &greatest);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&pipe->alt, cudaStreamNonBlocking);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->forked, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->joined, cudaEventDisableTiming);
-    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->costs_ready, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->forked, ev_flags);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->joined, ev_flags);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->costs_ready, ev_flags);
     for (int g = 0; g < kMaxGroups && e == cudaSuccess; ++g) {
         // highest priority: a wavefront CTA must get onto an SM as soon as a CTA of the streaming kernels retires
         e = cudaStreamCreateWithPriority(&pipe->side[g], cudaStreamNonBlocking, greatest);
-        if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&pipe->grad[g], cudaStreamNonBlocking, least);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->gathered[g], cudaEventDisableTiming);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->solved[g], cudaEventDisableTiming);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->graded[g], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->gathered[g], ev_flags);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->solved[g], ev_flags);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pipe->graded[g], ev_flags);
     }
     if (e != cudaSuccess) {
         fail_launch("pipe_create", e);
@@ -207,6 +208,27 @@ int cwrnnt_pipe_create(cwrnnt_pipe **out)
     }
     *out = pipe;
     return CWRNNT_OK;
+}
+
+int cwrnnt_pipe_create(cwrnnt_pipe **out) { return pipe_create(out, false); }
+int cwrnnt_pipe_create_traced(cwrnnt_pipe **out) { return pipe_create(out, true); }
+
+int cwrnnt_pipe_timeline(cwrnnt_pipe *pipe, float *ms, int32_t capacity)
+{
+    if (!pipe || !ms || capacity < 0) return -1;
+    if (!pipe->traced) return -1;
+    const int G = pipe->last_groups;
+    if (G < 2) return 0;  // an ungrouped step stays on the caller's stream and records no events
+    if (capacity < 3 * G) return -1;
+    for (int g = 0; g < G; ++g) {
+        cudaEvent_t ev[3] = {pipe->gathered[g], pipe->solved[g], pipe->graded[g]};
+        for (int k = 0; k < 3; ++k)
+            if (cudaEventElapsedTime(&ms[3 * g + k], pipe->forked, ev[k]) != cudaSuccess) {
+                cudaGetLastError();
+                ms[3 * g + k] = -1.0f;
+            }
+    }
+    return G;
 }
 
 void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe)
@@ -218,7 +240,6 @@ void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe)
     if (pipe->costs_ready) cudaEventDestroy(pipe->costs_ready);
     for (int g = 0; g < kMaxGroups; ++g) {
         if (pipe->side[g]) cudaStreamDestroy(pipe->side[g]);
-        if (pipe->grad[g]) cudaStreamDestroy(pipe->grad[g]);
         if (pipe->gathered[g]) cudaEventDestroy(pipe->gathered[g]);
         if (pipe->solved[g]) cudaEventDestroy(pipe->solved[g]);
         if (pipe->graded[g]) cudaEventDestroy(pipe->graded[g]);
@@ -252,12 +273,15 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
 
     const GroupPlan plan = plan_groups(*p, pipe ? groups : 1);
     const int G = plan.count;
+    if (pipe) pipe->last_groups = G;
     ShardOutput shard{global_ids, n_global, cost_vector};
 
-    // Streams. The streaming kernels of consecutive groups alternate between the caller's stream and pipe->alt: two
+    // Streams - few of them on purpose: a device serves its streams through a small number of hardware queues (8
+    // unless the process asks for more), and streams that share a queue wait for one another as if they were one. The
+    // step uses 2 + G: the gathers of consecutive ranges alternate between the caller's stream and pipe->alt (two
     // launches on one stream leave the SMs idle between the last CTAs of one and the first of the next, on two
-    // streams the next one's CTAs fill in as the previous one's run out (they touch different rows). The wavefront
-    // of group g runs on the high-priority stream side[g].
+    // streams the next one's CTAs fill in as the previous one's run out); group g's wavefront runs on the
+    // high-priority stream side[g]; the gradients reuse these streams (see below).
 #define CWRNNT_TRY(call, what) \
     if ((e = (call)) != cudaSuccess) return fail_launch(what, e)
     auto rows_stream = [&](int g) { return (G > 1 && (g & 1)) ? pipe->alt : s; };
@@ -281,42 +305,51 @@ int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, 
         CWRNNT_TRY(launch_wavefront(*p, lx, ly, w, costs, loss, cost_vector ? &shard : nullptr, k2, plan, g),
                    "wavefront");
         if (G > 1) CWRNNT_TRY(cudaEventRecord(pipe->solved[g], k2), "event");
+        if (pipe && G == 1) CWRNNT_TRY(cudaEventRecord(pipe->costs_ready, s), "event");  // before the gradient
     }
-    if (pipe) {
-        // costs, loss and the cost vector are final once every wavefront launch is done - before any gradient kernel
-        // has run. The event lets another stream (a collective on the cost vector) start from there.
-        cudaStream_t collect = G > 1 ? pipe->side[0] : s;
-        for (int g = 1; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(collect, pipe->solved[g], 0), "event");
-        CWRNNT_TRY(cudaEventRecord(pipe->costs_ready, collect), "event");
-    }
-    // The gradient of group g runs on its own stream behind `solved[g]` alone, so the groups' gradient launches start
-    // in the order in which their wavefronts finish, whatever the order of the rows: a group of short lattices that
-    // was gathered last is differentiated while the long chains of an earlier group are still running. Launches that
-    // are ready together are dispatched in issue order (group 0 first), each filling in as the one before runs out of
-    // CTAs, exactly as two alternating streams would.
+    // Where the gradient of group g is launched. Two schedules:
+    //  - in order, on the two gather streams alternately, each launch behind its group's wavefront (event): the
+    //    launches run back to back in group order, each filling in as the one before runs out of CTAs. Best when the
+    //    wavefronts are short next to the passes (narrow lattices): every wavefront but the last is long done;
+    //  - adaptive: behind the group's wavefront on that wavefront's own stream, so that the gradient launches start in
+    //    the order in which the wavefronts FINISH, whatever the order of the rows - a group of short lattices that was
+    //    gathered last is differentiated while the long chains of an earlier group are still running. For batches
+    //    whose wavefronts can outlast a pass: wide lattices, or a handful of long sequences.
+    const bool adaptive = G > 1 && (p->max_u + 1 > 256 || p->B <= 8);
     for (int g = 0; g < G; ++g) {
-        GradRows span{nullptr, 0, 0, 0};
+        GradRows span{nullptr, 0, 0, 0, false};
         cudaStream_t k3 = s;
         if (G > 1) {
-            k3 = pipe->grad[g];
-            CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->solved[g], 0), "event");
-            // the gathers that share rows with this group precede solved[g]; grad_x must also not be written before
-            // the caller's earlier work on `stream` is done
-            CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->forked, 0), "event");
-            // a group holds the sequences that END in its range, so it is about one range long, give or take a
-            // sequence: the grid is sized for one range and a longer group is finished by the same CTAs
+            k3 = adaptive ? pipe->side[g] : rows_stream(g);
+            if (adaptive) {
+                // not before the gather pass is over: a gradient kernel started earlier (a short group's wavefront is
+                // done in no time) would take bandwidth from the gathers that the other groups' wavefronts wait for
+                CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->gathered[G - 1], 0), "event");
+                CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->gathered[G - 2], 0), "event");
+            } else {
+                CWRNNT_TRY(cudaStreamWaitEvent(k3, pipe->solved[g], 0), "event");
+            }
+            // A group holds the sequences that END in its range, so it is about one range long, give or take a
+            // sequence: the grid is sized for one range and a longer group is finished by the same CTAs. On a
+            // wavefront's (high-priority) stream the launch itself asks for the lowest priority.
             const int64_t row0 = g * plan.range_rows;
-            span = GradRows{w.bounds + g, plan.range_rows, row0, g == G - 1 ? p->n_rows : row0 + plan.range_rows};
+            span = GradRows{w.bounds + g, plan.range_rows, row0, g == G - 1 ? p->n_rows : row0 + plan.range_rows,
+                            adaptive};
         }
         CWRNNT_TRY(launch_grad(*p, x, lx, ly, y, w, grad_costs, grad_costs_stride, grad_x, k3, span), "grad");
         if (G > 1) CWRNNT_TRY(cudaEventRecord(pipe->graded[g], k3), "event");
     }
     if (G > 1) {
-        // join: the gathers issued on alt, every gradient stream, and the collecting side stream (every wavefront
-        // stream is behind it)
+        // costs, loss and the cost vector are final once every wavefront launch is done - before the gradient kernels
+        // have finished. The event lets another stream (a collective on the cost vector) start from there; it is
+        // recorded on a stream of the pipe that carries no gradient launch.
+        cudaStream_t collect = adaptive ? pipe->alt : pipe->side[0];
+        for (int g = 0; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(collect, pipe->solved[g], 0), "event");
+        CWRNNT_TRY(cudaEventRecord(pipe->costs_ready, collect), "event");
+        // join: every gradient, pipe->alt (its gathers) and the costs-ready point
+        for (int g = 0; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->graded[g], 0), "event");
         CWRNNT_TRY(cudaEventRecord(pipe->joined, pipe->alt), "event");
         CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->joined, 0), "event");
-        for (int g = 0; g < G; ++g) CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->graded[g], 0), "event");
         CWRNNT_TRY(cudaStreamWaitEvent(s, pipe->costs_ready, 0), "event");
     }
 #undef CWRNNT_TRY

@@ -308,6 +308,30 @@ grad_rows_sparse_kernel(const T *__restrict__ x, T *__restrict__ gx, int V, RowR
     }
 }
 
+// A launch of a streaming kernel, optionally at the device's LOWEST priority whatever the stream's own (launch
+// attribute): in a pipelined step the gradient of a group follows the group's wavefront on that wavefront's
+// high-priority stream, and must not take SM slots from the wavefront CTAs of other groups that are still arriving.
+template <typename... KArgs, typename... Args>
+static void launch_rows(void (*kernel)(KArgs...), unsigned grid, cudaStream_t s, bool lowest_priority, Args... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kStreamThreads);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    if (lowest_priority) {
+        static const int lowest = [] {
+            int least = 0, greatest = 0;
+            return cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess ? least : 0;
+        }();
+        attr[0].id = cudaLaunchAttributePriority;
+        attr[0].val.priority = lowest;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);  // errors are picked up by cudaGetLastError below
+}
+
 template <typename T>
 static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int32_t *lx, const int32_t *ly,
                                  const int32_t *y, const Workspace &w, const void *grad_costs, int32_t gc_stride,
@@ -338,8 +362,8 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
     if (aligned && !pick_row_shape(p.V / VE, &shape)) {
         const int run_len = 4;  // long rows, in 4 KB segments: 32 rows per CTA
         const unsigned grid = tiled_grid(n_rows, int64_t(kStreamThreads / 32) * run_len);
-        grad_rows_long_kernel<T><<<grid, kStreamThreads, 0, s>>>(x, gx, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank,
-                                                                 p.flags, mean_inv, w, gc, gc_stride, run_len);
+        launch_rows(grad_rows_long_kernel<T>, grid, s, span.lowest_priority, x, gx, p.V, rows, p.B, lx, ly, y,
+                    p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride, run_len);
     } else if (aligned && pick_row_shape(p.V / VE, &shape)) {
         const bool full = (p.V / VE) == shape.lpr * shape.nv;
         // rows per lane group, measured 1..32 on B200: a tile of 8 rows x 4 KB (run 1) or 16 rows x 2 KB (run 2)
@@ -350,9 +374,8 @@ static cudaError_t launch_grad_t(const cwrnnt_problem &p, const T *x, const int3
 #define LAUNCH(LPR, NV, FULL)                                                                                    \
     {                                                                                                            \
         const unsigned grid = tiled_grid(n_rows, int64_t(kStreamThreads / LPR) * run_len);                       \
-        grad_rows_kernel<T, LPR, NV, FULL><<<grid, kStreamThreads, 0, s>>>(                                      \
-            x, gx, p.V, rows, p.B, lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride,          \
-            run_len);                                                                                            \
+        launch_rows(grad_rows_kernel<T, LPR, NV, FULL>, grid, s, span.lowest_priority, x, gx, p.V, rows, p.B,    \
+                    lx, ly, y, p.y_stride, p.blank, p.flags, mean_inv, w, gc, gc_stride, run_len);               \
     }
 #define CALL(LPR, NV)                    \
     {                                    \

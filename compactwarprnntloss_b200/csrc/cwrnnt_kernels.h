@@ -45,10 +45,11 @@ struct GradRows {
     const int64_t *device_range;
     int64_t grid_rows;
     int64_t nominal_begin, nominal_end;
+    bool lowest_priority;  // launch at the device's lowest priority whatever the stream's (dense logits-mode kernels)
 };
 cudaError_t launch_grad(const cwrnnt_problem &p, const void *x, const int32_t *lx, const int32_t *ly,
                         const int32_t *y, const Workspace &w, const void *grad_costs, int32_t gc_stride, void *grad_x,
-                        cudaStream_t s, const GradRows &span = GradRows{nullptr, 0, 0, 0});
+                        cudaStream_t s, const GradRows &span = GradRows{nullptr, 0, 0, 0, false});
 
 // grad_x *= *factor (a device scalar of the costs' type); returns at once on the device when the factor is 1.
 cudaError_t launch_scale(const cwrnnt_problem &p, void *grad_x, const void *factor, cudaStream_t s);

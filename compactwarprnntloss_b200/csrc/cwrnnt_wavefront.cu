@@ -292,7 +292,8 @@ struct WaveArgs {
     const int32_t *global_ids;
     int n_global;
     CostT *cost_vec;
-    // pipelined step: this launch runs the sequences of one group only; tickets are counted over all launches
+    // pipelined step: this launch runs the sequences of one group only; one completion ticket per sequence-direction
+    // over all launches of the step
     GroupPlan plan;
     int group;
     unsigned int ticket_total;
@@ -369,10 +370,9 @@ wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
     const int n = w.order[blockIdx.x / g.n_dirs];
-    if (other_group(g, n)) {  // one warp stays to take this CTA's completion ticket
-        if (threadIdx.x < 32) finalize_if_last(g, 32, edge, &last_flag);
-        return;
-    }
+    // Another launch's sequence: leave at once. Only CTAs that run a sequence-direction take a completion ticket (each
+    // sequence-direction runs in exactly one launch of the step), so leaving costs no atomic and no fence.
+    if (other_group(g, n)) return;
     const bool beta_dir = (g.n_dirs == 1) || (blockIdx.x & 1);
     const int T = g.lx[n], U = g.ly[n];
     const int64_t off = w.off[n];
@@ -531,10 +531,9 @@ wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::t
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
     const int n = w.order[blockIdx.x / g.n_dirs];
-    if (other_group(g, n)) {  // one warp stays to take this CTA's completion ticket
-        if (threadIdx.x < 32) finalize_if_last(g, 32, edge, &last_flag);
-        return;
-    }
+    // Another launch's sequence: leave at once. Only CTAs that run a sequence-direction take a completion ticket (each
+    // sequence-direction runs in exactly one launch of the step), so leaving costs no atomic and no fence.
+    if (other_group(g, n)) return;
     const bool beta_dir = (g.n_dirs == 1) || (blockIdx.x & 1);
     const int T = g.lx[n], U = g.ly[n];
     const int64_t off = w.off[n];
@@ -615,7 +614,7 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
     const int grid = p.B * g.n_dirs;
     g.plan = plan;
     g.group = group;
-    g.ticket_total = unsigned(grid) * unsigned(plan.count);
+    g.ticket_total = unsigned(grid);  // one ticket per sequence-direction, whichever launch of the step runs it
     cudaError_t e = cudaSuccess;
 
     if (cols <= 512) {

@@ -24,10 +24,14 @@ def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "
         wavefront is a chain of T+U dependent steps, so the longest chains must start first to finish underneath the
         streaming passes instead of after them. It is the sharding layer that decides a shard's row order, so this
         costs nothing.
+    ``order="pipeline"``  as longest_first, but led by the shortest chains - as many as hold an eighth of the rank's
+        rows. The gradient pass can begin only when SOME wavefront is done; a group of short lattices gathered first
+        has its wavefront done before the gather pass ends, so the gradient pass follows the gather pass without a
+        gap, while the long chains, gathered right after, still have the whole of both passes to hide under.
     ``order="ascending"``  ascending global index (each rank's compact rows stay in global order).
     """
-    if order not in ("longest_first", "ascending"):
-        raise ValueError("order must be 'longest_first' or 'ascending'")
+    if order not in ("longest_first", "pipeline", "ascending"):
+        raise ValueError("order must be 'longest_first', 'pipeline' or 'ascending'")
     if world < 1:
         raise ValueError("world must be >= 1")
     lx = [int(v) for v in lx]
@@ -43,7 +47,17 @@ def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "
         load[r] += lx[i] * (ly[i] + 1)
     if order == "ascending":
         return [sorted(ids) for ids in out]
-    return [sorted(ids, key=lambda i: (-(lx[i] + ly[i]), i)) for ids in out]
+    shards = [sorted(ids, key=lambda i: (-(lx[i] + ly[i]), i)) for ids in out]
+    if order == "pipeline":
+        for r, ids in enumerate(shards):
+            total = sum(lx[i] * (ly[i] + 1) for i in ids)
+            lead, rows = [], 0
+            while len(ids) > 1 and rows * 8 < total:
+                i = ids.pop()  # the shortest chain left
+                lead.append(i)
+                rows += lx[i] * (ly[i] + 1)
+            shards[r] = lead + ids
+    return shards
 
 
 def shard_imbalance(lx: Sequence[int], ly: Sequence[int], plan: List[List[int]]) -> float:

@@ -174,6 +174,18 @@ CWRNNT_API int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int
 typedef struct cwrnnt_pipe cwrnnt_pipe;
 CWRNNT_API int cwrnnt_pipe_create(cwrnnt_pipe **pipe);
 CWRNNT_API void cwrnnt_pipe_destroy(cwrnnt_pipe *pipe);
+/*
+ * Tracing of a pipelined step. A pipe from cwrnnt_pipe_create_traced records its events with timestamps (a pipe from
+ * cwrnnt_pipe_create does not: untimed events are cheaper). After the stream of the last cwrnnt_loss_grad has been
+ * synchronised, cwrnnt_pipe_timeline writes, for every sequence group g of that step, three times in milliseconds
+ * since the step's fork point (right after the row-offset kernel): ms[3g] = range g gathered, ms[3g+1] = wavefront of
+ * group g done, ms[3g+2] = gradient of group g done (-1 where an event is not available). Returns the number of
+ * groups (0 for an ungrouped step, which records nothing), or -1 on a bad argument, an untraced pipe or capacity
+ * below 3 * groups. The reference has no tracing (its only diagnostic is a device printf,
+ * cwarp_cuda_rnnt_kernel.cu:361).
+ */
+CWRNNT_API int cwrnnt_pipe_create_traced(cwrnnt_pipe **pipe);
+CWRNNT_API int cwrnnt_pipe_timeline(cwrnnt_pipe *pipe, float *ms, int32_t capacity);
 CWRNNT_API int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, const void *x, const int32_t *lx,
                                 const int32_t *ly, const int32_t *y, void *workspace, int64_t workspace_bytes,
                                 void *costs, void *loss, const void *grad_costs, int32_t grad_costs_stride,

@@ -87,6 +87,25 @@ def test_sequences_longer_than_a_range_and_empty_groups(pipe):
         _same(g0, g1)
 
 
+def test_traced_pipe_reports_a_timeline(pipe):
+    """A pipe created with tracing reports, per sequence group of the last step, when its range was gathered, its
+    wavefront done and its gradient done; results are the same as through an untraced pipe."""
+    case = ragged_case(12, 30, (20, 70), (3, 130), V=64, sigma=2.0)
+    args = _setup(case)
+    c0, l0, g0 = _two_calls(*args)
+    traced = capi.Pipe(DEV, traced=True)
+    c1, l1, g1, _ = _one_call(traced, *args, groups=3)
+    _same(c0, c1)
+    _same(g0, g1)
+    tl = traced.timeline()
+    assert len(tl) == 3 and all(0 < a <= b <= c for a, b, c in tl)
+    _one_call(traced, *args, groups=1)
+    assert traced.timeline() == []       # an ungrouped step stays on the caller's stream: nothing to report
+    traced.close()
+    with pytest.raises(capi.CwrnntError):
+        pipe.timeline()  # an untraced pipe has no timestamps
+
+
 def test_single_sequence(pipe):
     case = ragged_case(2, 1, (150, 150), (40, 40), V=128)
     args = _setup(case)
