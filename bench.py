@@ -66,7 +66,7 @@ def parse():
                     help="weak: B*N sequences over N GPUs (default); strong: the workload's B sequences sharded over N")
     ap.add_argument("--groups", type=int, default=0,
                     help="sequence groups of the pipelined step (0 = chosen by the library, 1 = no overlap)")
-    ap.add_argument("--order", default="longest_first", choices=["longest_first", "pipeline", "ascending"],
+    ap.add_argument("--order", default="pipeline", choices=["longest_first", "pipeline", "ascending"],
                     help="row order of a rank's sequences (sharding.plan_shards)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -12,19 +12,19 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 
 
-def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "longest_first") -> List[List[int]]:
+def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "pipeline") -> List[List[int]]:
     """Longest-processing-time-first assignment of sequences to ``world`` ranks.
 
     Weight of a sequence = its lattice size T*(U+1) (streaming cost is proportional to it for a fixed V); ties are
     broken by the wavefront critical path T+U, then by index, so every rank computes the same plan. Returns the global
     sequence ids of each rank in the order the rank should lay its rows out in memory:
 
-    ``order="longest_first"`` (default)  descending T+U, ties by index. The pipelined step cuts a rank's rows into
+    ``order="longest_first"``  descending T+U, ties by index. The pipelined step cuts a rank's rows into
         groups in memory order and starts the alpha/beta wavefront of a group as soon as its rows are gathered; a
         wavefront is a chain of T+U dependent steps, so the longest chains must start first to finish underneath the
         streaming passes instead of after them. It is the sharding layer that decides a shard's row order, so this
         costs nothing.
-    ``order="pipeline"``  as longest_first, but led by the shortest chains - as many as hold an eighth of the rank's
+    ``order="pipeline"`` (default)  as longest_first, but led by the shortest chains - as many as hold a sixteenth of the rank's
         rows. The gradient pass can begin only when SOME wavefront is done; a group of short lattices gathered first
         has its wavefront done before the gather pass ends, so the gradient pass follows the gather pass without a
         gap, while the long chains, gathered right after, still have the whole of both passes to hide under.
@@ -52,7 +52,7 @@ def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "
         for r, ids in enumerate(shards):
             total = sum(lx[i] * (ly[i] + 1) for i in ids)
             lead, rows = [], 0
-            while len(ids) > 1 and rows * 8 < total:
+            while len(ids) > 1 and rows * 16 < total:
                 i = ids.pop()  # the shortest chain left
                 lead.append(i)
                 rows += lx[i] * (ly[i] + 1)

@@ -17,9 +17,18 @@ def test_plan_is_balanced_deterministic_and_complete():
         plan = sharding.plan_shards(lx.tolist(), ly.tolist(), world)
         sharding.validate_plan(plan, len(lx))
         assert plan == sharding.plan_shards(lx.tolist(), ly.tolist(), world)
-        # default row order of a shard: longest critical path (T+U) first, so its wavefront starts first
+        # longest critical path (T+U) first, so its wavefront starts first
         chain = (lx + ly).tolist()
-        assert all(all(chain[a] >= chain[b] for a, b in zip(ids, ids[1:])) for ids in plan)
+        longest = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order="longest_first")
+        assert all(all(chain[a] >= chain[b] for a, b in zip(ids, ids[1:])) for ids in longest)
+        # default: the same, led by the shortest chains holding about a sixteenth of the shard's rows
+        rows = (lx.long() * (ly.long() + 1)).tolist()
+        for ids, ref in zip(plan, longest):
+            assert sorted(ids) == sorted(ref)
+            k = next(i for i in range(1, len(ids)) if chain[ids[i]] > chain[ids[i - 1]] + 0 and chain[ids[i]] == chain[ref[0]])
+            lead = ids[:k]
+            assert all(chain[a] <= chain[b] for a, b in zip(lead, lead[1:])) and ids[k:] == ref[:len(ref) - k]
+            assert sum(rows[i] for i in lead[:-1]) * 16 < sum(rows[i] for i in ids)
         asc = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order="ascending")
         assert [sorted(ids) for ids in plan] == asc and all(ids == sorted(ids) for ids in asc)
         assert sharding.shard_imbalance(lx, ly, plan) < 1.05
