@@ -68,6 +68,9 @@ def parse():
                     help="sequence groups of the pipelined step (0 = chosen by the library, 1 = no overlap)")
     ap.add_argument("--order", default="pipeline", choices=["longest_first", "pipeline", "ascending"],
                     help="row order of a rank's sequences (sharding.plan_shards)")
+    ap.add_argument("--sequences", type=int, default=0,
+                    help="use only the first N sequences of the workload (0 = all): a smaller case of the same "
+                         "kernels for a profiler capture, not a benchmark configuration")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the other workloads (N = 1 only)")
@@ -176,12 +179,12 @@ def host_threads():
         return os.cpu_count() or 1
 
 
-def workload_config(cfg, world, scaling, order):
+def workload_config(cfg, world, scaling, order, sequences=0):
     """The `config` object of the JSON line, from the lengths alone - the same for this engine's arm and for the CPU
     reference arm, so that the two lines name one workload."""
     from compactwarprnntloss_b200 import sharding
     wl = synth.WORKLOADS[cfg]
-    B_global = wl.B * world if scaling == "weak" else wl.B
+    B_global = (sequences or wl.B) * (world if scaling == "weak" else 1)
     lx, ly, _ = synth.lengths_and_labels(cfg, B=B_global)
     plan = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order=order)
     elt = torch.empty((), dtype=wl.dtype).element_size()
@@ -250,7 +253,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": DTYPE_NAME[wl.dtype], "data": "synthetic",
-        "config": workload_config(cfg, world, args.scaling, args.order),
+        "config": workload_config(cfg, world, args.scaling, args.order, args.sequences),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -556,7 +559,7 @@ def main():
 
     # ---- headline workload: weak scaling, B = wl.B * world sequences sharded by lattice size, host-generated (the
     # e2e leg and the CPU baseline need the same logits in host memory)
-    B_global = wl.B * world if args.scaling == "weak" else wl.B
+    B_global = (args.sequences or wl.B) * (world if args.scaling == "weak" else 1)
     lx, ly, y = synth.lengths_and_labels(cfg, B=B_global)
     plan = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order=args.order)
     sharding.validate_plan(plan, B_global)
@@ -711,7 +714,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": DTYPE_NAME[wl.dtype], "data": "synthetic",
-        "config": workload_config(cfg, world, args.scaling, args.order),
+        "config": workload_config(cfg, world, args.scaling, args.order, args.sequences),
         "timing": {"blocks": repeats, "steps_per_block": K, "ms_per_step_median": sp["median"],
                    "ms_per_step_min": sp["min"], "ms_per_step_max": sp["max"],
                    "timed_region_ms": sum(blocks),

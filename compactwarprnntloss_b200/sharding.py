@@ -24,10 +24,13 @@ def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "
         wavefront is a chain of T+U dependent steps, so the longest chains must start first to finish underneath the
         streaming passes instead of after them. It is the sharding layer that decides a shard's row order, so this
         costs nothing.
-    ``order="pipeline"`` (default)  as longest_first, but led by the shortest chains - as many as hold a sixteenth of the rank's
-        rows. The gradient pass can begin only when SOME wavefront is done; a group of short lattices gathered first
-        has its wavefront done before the gather pass ends, so the gradient pass follows the gather pass without a
-        gap, while the long chains, gathered right after, still have the whole of both passes to hide under.
+    ``order="pipeline"`` (default)  longest_first, except that a shard of at most 8 sequences (the size below which
+        the pipelined step gives every sequence a group of its own) is led by its SHORTEST sequence. The gradient pass
+        can begin only when some wavefront is done; with a handful of long lattices the first one gathered is the
+        first one done, so the shortest goes first and the gradient pass follows the gather pass without a gap
+        (measured on 4 x [1250 x 300] x 512: 1.49 ms per step against 1.56), while the longest, gathered right after
+        it, still has both passes to hide under. With many sequences per group a group is as slow as its longest
+        chain, and a lead of short ones buys nothing (ragged 256-sequence batch: 0.71 ms against 0.68).
     ``order="ascending"``  ascending global index (each rank's compact rows stay in global order).
     """
     if order not in ("longest_first", "pipeline", "ascending"):
@@ -50,13 +53,8 @@ def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "
     shards = [sorted(ids, key=lambda i: (-(lx[i] + ly[i]), i)) for ids in out]
     if order == "pipeline":
         for r, ids in enumerate(shards):
-            total = sum(lx[i] * (ly[i] + 1) for i in ids)
-            lead, rows = [], 0
-            while len(ids) > 1 and rows * 16 < total:
-                i = ids.pop()  # the shortest chain left
-                lead.append(i)
-                rows += lx[i] * (ly[i] + 1)
-            shards[r] = lead + ids
+            if 1 < len(ids) <= 8:
+                shards[r] = [ids[-1]] + ids[:-1]
     return shards
 
 

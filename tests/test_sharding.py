@@ -21,17 +21,16 @@ def test_plan_is_balanced_deterministic_and_complete():
         chain = (lx + ly).tolist()
         longest = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order="longest_first")
         assert all(all(chain[a] >= chain[b] for a, b in zip(ids, ids[1:])) for ids in longest)
-        # default: the same, led by the shortest chains holding about a sixteenth of the shard's rows
-        rows = (lx.long() * (ly.long() + 1)).tolist()
+        # default: the same, except that a shard of at most 8 sequences is led by its shortest one
         for ids, ref in zip(plan, longest):
-            assert sorted(ids) == sorted(ref)
-            k = next(i for i in range(1, len(ids)) if chain[ids[i]] > chain[ids[i - 1]] + 0 and chain[ids[i]] == chain[ref[0]])
-            lead = ids[:k]
-            assert all(chain[a] <= chain[b] for a, b in zip(lead, lead[1:])) and ids[k:] == ref[:len(ref) - k]
-            assert sum(rows[i] for i in lead[:-1]) * 16 < sum(rows[i] for i in ids)
+            assert ids == ([ref[-1]] + ref[:-1] if 1 < len(ref) <= 8 else ref)
         asc = sharding.plan_shards(lx.tolist(), ly.tolist(), world, order="ascending")
         assert [sorted(ids) for ids in plan] == asc and all(ids == sorted(ids) for ids in asc)
         assert sharding.shard_imbalance(lx, ly, plan) < 1.05
+    lx4, ly4, _ = synth.lengths_and_labels(4)
+    few = sharding.plan_shards(lx4.tolist(), ly4.tolist(), 1)[0]
+    chain4 = (lx4 + ly4).tolist()
+    assert chain4[few[0]] == min(chain4) and chain4[few[1]] == max(chain4)
     lx2, ly2, _ = synth.lengths_and_labels(2, B=64)
     assert sharding.shard_imbalance(lx2, ly2, sharding.plan_shards(lx2, ly2, 8)) < 1.05
 
