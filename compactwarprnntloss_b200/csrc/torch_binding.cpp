@@ -107,7 +107,9 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> rnnt_forward(const torch
     cwrnnt_problem p = describe(xs, lx, ys, blank, flags, mean_denominator);
     auto ws = make_workspace(p, xs);
     auto costs = torch::empty({lx.size(0)}, xs.options().dtype(cost_type(xs)));
-    auto loss = torch::zeros({}, costs.options());
+    // written by the kernels whenever a reduction is asked for on a non-empty batch (NaN on invalid lengths)
+    auto loss = ((flags & (CWRNNT_REDUCE_MEAN | CWRNNT_REDUCE_SUM)) && lx.size(0) > 0) ? torch::empty({}, costs.options())
+                                                                   : torch::zeros({}, costs.options());
     check_status(cwrnnt_forward(&p, xs.data_ptr(), i32(lx), i32(ly), i32(ys), ws.data_ptr(), ws.numel(),
                                 costs.data_ptr(), loss.data_ptr(), current_stream()),
                  "cwrnnt_forward");
@@ -153,7 +155,9 @@ rnnt_loss_grad(const torch::Tensor &xs, const torch::Tensor &lx, const torch::Te
     cwrnnt_problem p = describe(xs, lx, ys, blank, flags, mean_denominator);
     auto ws = make_workspace(p, xs);
     auto costs = torch::empty({lx.size(0)}, xs.options().dtype(cost_type(xs)));
-    auto loss = torch::zeros({}, costs.options());
+    // written by the kernels whenever a reduction is asked for on a non-empty batch (NaN on invalid lengths)
+    auto loss = ((flags & (CWRNNT_REDUCE_MEAN | CWRNNT_REDUCE_SUM)) && lx.size(0) > 0) ? torch::empty({}, costs.options())
+                                                                   : torch::zeros({}, costs.options());
     auto gx = torch::empty_like(xs);
     check_status(cwrnnt_loss_grad(pipe_of(xs.get_device()), &p, xs.data_ptr(), i32(lx), i32(ly), i32(ys),
                                   ws.data_ptr(), ws.numel(), costs.data_ptr(), loss.data_ptr(), nullptr, 0,
