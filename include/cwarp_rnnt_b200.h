@@ -157,12 +157,16 @@ CWRNNT_API int cwrnnt_backward(const cwrnnt_problem *p, const void *x, const int
  * during the forward call and backward only scales them (cwarp_rnnt/__init__.py:10-29, cwarp_cuda.cpp:84-136) - and,
  * with CWRNNT_FUSED_LOG_SOFTMAX, the caller's log_softmax forward and backward.
  * The rows are cut into `groups` ranges; group g = the sequences whose last row lies in range g. On the caller's
- * stream and one more stream of the pipe, alternating: K0, the gather of range 0..G-1, then the gradient of group
- * 0..G-1. On the pipe's high-priority side streams: the alpha/beta wavefront of group g as soon as ranges 0..g are
- * gathered. The wavefront (a chain of T+U dependent steps on a few SMs) thereby runs underneath the two
- * bandwidth-bound passes instead of between them. Everything is joined back into `stream` before the call returns
+ * stream and one more stream of the pipe, alternating: K0, then the gather of range 0..G-1. On the pipe's
+ * high-priority side stream g: the alpha/beta wavefront of group g as soon as ranges 0..g are gathered. The gradient
+ * of group g follows its wavefront - in group order on the two gather streams for batches of narrow lattices, on side
+ * stream g itself (so in the order in which the wavefronts finish, at the lowest launch priority) when max_u + 1 > 256
+ * or B <= 8, where one wavefront can outlast a pass. The wavefront (a chain of T+U dependent steps on a few SMs)
+ * thereby runs underneath the two bandwidth-bound passes instead of between them. The step uses 2 + G streams, few
+ * enough for the device's hardware queues. Everything is joined back into `stream` before the call returns
  * (event waits, nothing blocks the host), so results are ordered on `stream` exactly like those of cwrnnt_forward +
- * cwrnnt_backward; they are bit-identical to that pair's.
+ * cwrnnt_backward; they are bit-identical to that pair's. Rows laid out with the longest T+U first start the longest
+ * chains first (sharding.plan_shards does that for a shard).
  *   pipe        side streams and events, from cwrnnt_pipe_create on the same device; one call at a time per pipe.
  *               NULL runs the same work on `stream` alone without overlap.
  *   grad_costs / grad_costs_stride / grad_x   as cwrnnt_backward (NULL grad_costs: upstream gradient 1)
@@ -194,7 +198,7 @@ CWRNNT_API int cwrnnt_loss_grad(cwrnnt_pipe *pipe, const cwrnnt_problem *p, cons
 
 /*
  * Makes `stream` wait until the costs, the loss and the cost vector of the last cwrnnt_loss_grad issued through
- * `pipe` are written - which is before its gradient kernels run. A sharded caller puts its all-reduce of the cost
+ * `pipe` are written - which is before its gradient kernels are done. A sharded caller puts its all-reduce of the cost
  * vector on a second stream behind this wait, so the collective runs underneath the gradient pass instead of after
  * it. No counterpart in the reference (single GPU).
  */
