@@ -106,6 +106,40 @@ def test_traced_pipe_reports_a_timeline(pipe):
         pipe.timeline()  # an untraced pipe has no timestamps
 
 
+@pytest.mark.parametrize("shape", [(6, (30, 90), (5, 40)), (12, (10, 40), (100, 300))])
+def test_adaptive_gradient_schedule_is_bit_identical_and_capturable(pipe, shape):
+    """Batches of at most 8 sequences, or with lattices wider than 256 columns, queue each group's gradient behind the
+    group's wavefront on that wavefront's own stream (at the lowest launch priority) instead of in group order. Same
+    results bit for bit, and the whole step - priority attribute included - can be captured and replayed."""
+    B, Tr, Ur = shape
+    case = ragged_case(77 + B, B, Tr, Ur, V=64, sigma=1.5)
+    args = _setup(case)
+    p, x, lx, ly, y = args
+    assert p.B <= 8 or p.max_u + 1 > 256
+    c0, l0, g0 = _two_calls(*args)
+    for groups in (2, 3, 4):
+        c1, l1, g1, _ = _one_call(pipe, *args, groups=groups)
+        _same(c0, c1)
+        _same(l0, l1)
+        _same(g0, g1)
+    ws = capi.alloc_workspace(p, DEV)
+    costs, loss, gx = torch.empty(p.B, device=DEV), torch.empty((), device=DEV), torch.empty_like(x)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            capi.loss_grad(p, x, lx, ly, y, ws, costs, loss, None, 0, gx, pipe=pipe, groups=3)
+    torch.cuda.synchronize()
+    for _ in range(2):
+        costs.fill_(float("nan"))
+        gx.fill_(float("nan"))
+        graph.replay()
+        torch.cuda.synchronize()
+        _same(c0, costs)
+        _same(l0, loss)
+        _same(g0, gx)
+
+
 def test_single_sequence(pipe):
     case = ragged_case(2, 1, (150, 150), (40, 40), V=128)
     args = _setup(case)
