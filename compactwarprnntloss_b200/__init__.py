@@ -7,6 +7,7 @@ Sub-modules:
   synth     seeded synthetic workloads of the benchmark configurations
   joint     `compact_joint` - the joint network's broadcast-add written directly as compact rows
   graphs    `GraphedStep` - a whole training step of the loss as one replayed CUDA graph per shape bucket
+  analysis  `analyse` - best alignment, node posteriors and padded alpha / beta from a forward pass
   build     in-tree build of the native parts
 
 Importing the package itself is light and works on a machine without a GPU; `loss` and `capi.lib()` raise if the
@@ -22,6 +23,9 @@ def __getattr__(name):
     if name == "GraphedStep":
         from . import graphs
         return graphs.GraphedStep
+    if name in ("analyse", "LatticeAnalysis"):
+        from . import analysis
+        return getattr(analysis, name)
     if name == "compact_joint":
         from . import joint
         return joint.compact_joint

@@ -90,3 +90,36 @@ def test_node_posteriors_against_oracle(oracle, dtype):
         for d in range(T + m - 1):  # every alignment crosses each anti-diagonal exactly once
             s = sum(got[t, d - t] for t in range(T) if 0 <= d - t < m)
             assert abs(s - 1) <= 2e-5
+
+
+def test_python_level_analysis(oracle):
+    """`compactwarprnntloss_b200.analyse`: one call from compact logits to costs, best path, posteriors and padded
+    alpha / beta; the emission frames derived from the path agree with the oracle's path."""
+    from compactwarprnntloss_b200 import analyse
+    case = ragged_case(29, 4, (5, 40), (1, 12), V=16, sigma=1.5)
+    dev = "cuda:0"
+    x = torch.as_tensor(case["x"]).to(dev)
+    lx, ly = torch.as_tensor(case["lx"]).to(dev), torch.as_tensor(case["ly"]).to(dev)
+    y = torch.as_tensor(case["y"]).to(dev)
+    res = analyse(x, lx, y, ly, 0, fused_log_softmax=True, want_alpha_beta=True)
+    g = oracle.gather(oracle.log_softmax(case["x"]), case["lx"], case["ly"], case["y"], 0)
+    want_moves, want_scores = oracle.viterbi(g, case["lx"], case["ly"])
+    fw = oracle.forward(g, case["lx"], case["ly"], want_ab=True)
+    np.testing.assert_allclose(res.costs.cpu().numpy(), fw["costs"], rtol=1e-5)
+    np.testing.assert_allclose(res.path_log_prob.cpu().numpy(), want_scores, rtol=1e-5, atol=1e-5)
+    Tm, Up = int(case["lx"].max()), int(case["ly"].max()) + 1
+    assert res.posteriors.shape == (4, Tm, Up) and res.alphas.shape == (4, Tm, Up)
+    for n in range(4):
+        T, U = int(case["lx"][n]), int(case["ly"][n])
+        mv = want_moves[n, :T + U]
+        want_frames = np.cumsum(mv == 0)[mv == 1]
+        got_frames = res.emission_frames(n).cpu().numpy()
+        assert got_frames.shape == (U,) and np.all(np.diff(got_frames) >= 0) and np.all(got_frames < T)
+        if np.array_equal(res.moves[n, :T + U].cpu().numpy(), mv):
+            assert np.array_equal(got_frames, want_frames)
+        o = fw["offset"][n]
+        np.testing.assert_allclose(res.alphas[n, :T, :U + 1].cpu().numpy(),
+                                   fw["alpha"][o:o + T * (U + 1)].reshape(T, U + 1), rtol=1e-5, atol=1e-5)
+        assert abs(float(res.posteriors[n, 0, 0]) - 1) < 1e-5 and abs(float(res.posteriors[n, T - 1, U]) - 1) < 1e-5
+    with pytest.raises(ValueError):
+        analyse(x[:-1], lx, y, ly, 0, fused_log_softmax=True)
