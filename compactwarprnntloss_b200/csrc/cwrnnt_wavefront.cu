@@ -406,6 +406,10 @@ wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g
 // registers); the helper refills slot s % R during step s, after its last read during step s-1. Step 0's operands
 // are read before the loop, between two start barriers, so that the refill of slot 0 during step 0 cannot overtake
 // that read.
+constexpr int kRoundsMinCols = 160;  // padded column count above which a launch uses rounds
+constexpr int kRoundsRing = 16;      // operand slots of the rounds variant
+constexpr int kRoundsRows = 8;       // result rows of the rounds variant
+
 template <int R, bool F64, bool BETA>
 __device__ __forceinline__ void run_direction_split(int T, int U, const double *__restrict__ lpb,
                                                     const double *__restrict__ lpl, double *__restrict__ out,
@@ -519,7 +523,141 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
     }
 }
 
-template <int R, bool F64>
+// ------------------------------------------------------------------------------------------------ split-role, rounds
+// Wide lattices (more than kRoundsMinCols columns). With many warps in the CTA the step's barrier is the costly part,
+// and the helpers do not need to meet the compute warps on every step. Here the compute warps close a step on a
+// barrier of their own (half the threads), and helpers and compute warps meet once per round of Q steps:
+//   ring of R = 16 operand slots (step x in slot x % R), V = 8 result rows (step x in row x % V);
+//   round r, compute warps: steps Qr .. Qr+Q-1, operands read one step ahead as above;
+//   round r, helper warps : for x = Qr-Q+1 .. Qr, store the result of step x-1 (written during round r-1) and refill
+//                           the slot of step x (read during round r-1 at the latest) with the operands of step x+R.
+// At the barrier that ends round r the operands of steps up to Qr+2Q are needed; they were issued in round r-2 at the
+// latest, so one copy group per round and `wait_group 2` leave every copy between two and three rounds to land. The
+// prologue stages steps 0 .. R-Q and the first round continues from there. Rows of results live for two rounds: the
+// compute warps write row x % V again Q*2 = V steps later, after the barrier that ends the round in which the helpers
+// read it. Measured against the per-step barrier above: 0.194 vs 0.218 us per diagonal at 256 columns, 0.306 vs
+// 0.352 at 512; equal near 150 columns and a few per cent slower below (more shared memory, longer prologue). The
+// double-precision recursion (libm exp/log1p on the chain) measured slower this way up to 384 columns (0.84 vs 0.73 us
+// per diagonal at 256) and stays on the per-step barrier.
+template <bool F64, bool BETA>
+__device__ __forceinline__ void run_direction_rounds(int T, int U, const double *__restrict__ lpb,
+                                                     const double *__restrict__ lpl, double *__restrict__ out,
+                                                     double *__restrict__ ll_out, int n_cols, int n_sync,
+                                                     double *stage, double *vbuf,
+                                                     const float4 *__restrict__ lse_tab, bool helper, int u)
+{
+    constexpr int R = kRoundsRing, Q = 4, V = kRoundsRows;
+    const int m = U + 1;
+    const int nd = T + U;
+    const int n_rounds = (nd + Q - 1) / Q;
+    double *st_b = stage + u;
+    double *st_l = stage + R * n_cols + u;
+    const int vstride = n_cols + 1;
+
+    if (helper) {
+        const int c2 = (U <= T - 1) ? U + 1 : T - 1;
+        int e = BETA ? nd - 1 : -1;
+        int base = BETA ? T * m - 1 - U : 0;
+        int tb = u <= U ? e - u : INT_MIN / 2;
+        int sbase[R];
+#pragma unroll
+        for (int k = 0; k < R; ++k) sbase[k] = 0;
+        auto issue = [&](int k) {
+            sbase[k] = base;
+            double *sb = st_b + k * n_cols, *sl = st_l + k * n_cols;
+            if (!BETA) {
+                if (unsigned(tb) < unsigned(T - 1)) cp_async8(sb, lpb + base + u); else *sb = 0.0;
+                if (u >= 1 && unsigned(tb + 1) < unsigned(T)) cp_async8(sl, lpl + base + u - 1); else *sl = 0.0;
+                if (e >= 0) base += min(min(e + 1, c2), U + T - 1 - e);
+                ++e;
+                ++tb;
+            } else {
+                const bool cell = unsigned(tb) < unsigned(T);
+                if (cell) cp_async8(sb, lpb + base + u); else *sb = 0.0;
+                if (cell && u < U) cp_async8(sl, lpl + base + u); else *sl = 0.0;
+                --e;
+                --tb;
+                if (e >= 0) base -= min(min(e + 1, c2), U + T - 1 - e);
+            }
+        };
+#pragma unroll
+        for (int k = 0; k <= R - Q; ++k) issue(k);  // steps 0 .. R-Q
+        cp_async_commit();
+        cp_async_wait<0>();
+        // frame index of this column at step x-1, for x = -(Q-1)
+        int tprev = u <= U ? (BETA ? nd - u + (Q - 1) : -u - 1 - (Q - 1)) : INT_MIN / 2;
+        int last_base = 0;
+        asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+        asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+        // round r (compute runs steps Qr .. Qr+Q-1): x = Qr-(Q-1) .. Qr; store the result of step x-1 (previous round),
+        // then refill the slot of step x with the operands of step x+R
+        bool done = false;
+        for (int s0 = 0; !done; s0 += R) {
+#pragma unroll
+            for (int q = 0; q < R / Q; ++q) {
+                const bool drain = (s0 + Q * q) >= Q * n_rounds;
+#pragma unroll
+                for (int j = 0; j < Q; ++j) {
+                    constexpr int RQ = R - Q + 1;
+                    const int slot = (Q * q + j + RQ) % R;
+                    const int row = (Q * q + j + V - Q) % V;
+                    const int this_base = sbase[slot];
+                    const int out_base = BETA ? last_base : this_base;
+                    last_base = this_base;
+                    if (unsigned(tprev) < unsigned(T)) out[out_base + u] = vbuf[row * vstride + u];
+                    tprev += BETA ? -1 : 1;
+                    if (!drain) issue(slot);
+                }
+                if (drain) { done = true; break; }
+                cp_async_commit();
+                cp_async_wait<2>();
+                asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+            }
+        }
+        cp_async_wait<0>();
+        return;
+    }
+
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        vbuf[i * vstride + u] = -INFINITY;
+        if (u == 0) vbuf[i * vstride + n_cols] = -INFINITY;
+    }
+    double prev = (u == (BETA ? U : 0)) ? 0.0 : -INFINITY;
+    const int nb_col = BETA ? (u >= U ? n_cols : u + 1) : (u == 0 ? n_cols : u - 1);
+    asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+    double cur_b = st_b[0], cur_l = st_l[0];
+    asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+    for (int s0 = 0; s0 < nd; s0 += R) {
+#pragma unroll
+        for (int q = 0; q < R / Q; ++q) {
+            if (s0 + Q * q >= nd) break;
+#pragma unroll
+            for (int j = 0; j < Q; ++j) {
+                const int k = Q * q + j;
+                if (s0 + k < nd) {
+                    const double nxt_b = st_b[((k + 1) % R) * n_cols];
+                    const double nxt_l = st_l[((k + 1) % R) * n_cols];
+                    const double nb = vbuf[((k + V - 1) % V) * vstride + nb_col];
+                    const double v = lse2<F64>(prev + cur_b, nb + cur_l, lse_tab);
+                    vbuf[(k % V) * vstride + u] = v;
+                    prev = v;
+                    cur_b = nxt_b;
+                    cur_l = nxt_l;
+                }
+                if (j < Q - 1) asm volatile("bar.sync 2, %0;" ::"r"(n_cols) : "memory");
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
+        }
+    }
+    if (!BETA) {
+        if (u == U) *ll_out = prev + __ldg(lpb + int64_t(T) * m - 1);
+    } else {
+        if (u == 0) *ll_out = prev;
+    }
+}
+
+template <int R, bool F64, bool ROUNDS>
 __global__ void __launch_bounds__(1024)
 wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g)
 {
@@ -549,12 +687,21 @@ wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::t
     if (!F64) build_lse_table(lse_tab, vtid, n_sync);
     asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
     double *vbuf = stage + 2 * R * n_cols;
-    if (beta_dir)
-        run_direction_split<R, F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n,
-                                          n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
-    else
-        run_direction_split<R, F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off, w.ll_alpha + n,
-                                           n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+    if constexpr (ROUNDS) {
+        if (beta_dir)
+            run_direction_rounds<F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n,
+                                            n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+        else
+            run_direction_rounds<F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off, w.ll_alpha + n,
+                                             n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+    } else {
+        if (beta_dir)
+            run_direction_split<R, F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n,
+                                              n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+        else
+            run_direction_split<R, F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off,
+                                               w.ll_alpha + n, n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+    }
     // the compute warps finalise (helpers are done; n_cols threads with dense ids 0..n_cols-1)
     if (is_helper) return;
     finalize_if_last(g, n_cols, edge, &last_flag);
@@ -586,6 +733,36 @@ template <typename K>
 static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
 {
     return opt_in_smem_impl(reinterpret_cast<const void *>(kernel), smem, threads);
+}
+
+// True when `grid` CTAs of `threads` threads and `smem` bytes of dynamic shared memory are all resident at once. The
+// rounds variant takes 2.2 times the shared memory of the per-step one; on a launch that no longer fits the device in
+// one wave the second wave costs more than the cheaper barrier saves (512 CTAs of 256 columns: 234 us against 226 us).
+static bool one_wave(int grid, int threads, size_t smem)
+{
+    struct Limits { int sms = 0, smem_per_sm = 0; };
+    static std::mutex lock;
+    static std::map<int, Limits> seen;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return false;
+    Limits lim;
+    {
+        std::lock_guard<std::mutex> hold(lock);
+        Limits &l = seen[device];
+        if (l.sms == 0) {
+            if (cudaDeviceGetAttribute(&l.sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+                cudaDeviceGetAttribute(&l.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device) !=
+                    cudaSuccess) {
+                l = Limits{};
+                return false;
+            }
+        }
+        lim = l;
+    }
+    const size_t per_cta = smem + 10 * 1024;  // static arrays of the kernel (8.6 KB) and the per-CTA reserve (1 KB)
+    const int by_smem = int(size_t(lim.smem_per_sm) / per_cta);
+    const int by_threads = 2048 / threads;
+    return int64_t(grid) <= int64_t(lim.sms) * (by_smem < by_threads ? by_smem : by_threads);
 }
 
 template <bool F64>
@@ -623,8 +800,17 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
         const int half = (cols + 31) & ~31;
         const int threads = 2 * half;
         const size_t smem = (size_t(2 * R + 2) * half + 2) * sizeof(double);
-        if ((e = opt_in_smem(wavefront_split_kernel<R, F64>, smem, threads)) != cudaSuccess) return e;
-        wavefront_split_kernel<R, F64><<<grid, threads, smem, s>>>(g);
+        const size_t wide = (size_t(2 * kRoundsRing + kRoundsRows) * half + kRoundsRows) * sizeof(double);
+        if constexpr (!F64) {
+            if (half > kRoundsMinCols && one_wave(grid, threads, wide)) {
+                if ((e = opt_in_smem(wavefront_split_kernel<kRoundsRing, false, true>, wide, threads)) != cudaSuccess)
+                    return e;
+                wavefront_split_kernel<kRoundsRing, false, true><<<grid, threads, wide, s>>>(g);
+                return cudaGetLastError();
+            }
+        }
+        if ((e = opt_in_smem(wavefront_split_kernel<R, F64, false>, smem, threads)) != cudaSuccess) return e;
+        wavefront_split_kernel<R, F64, false><<<grid, threads, smem, s>>>(g);
         return cudaGetLastError();
     }
     const int C = cols <= 1024 ? 1 : (cols <= 2048 ? 4 : 8);

@@ -101,6 +101,22 @@ def test_wide_and_long_lattices(oracle, T, U):
     _check_fused(oracle, case)
 
 
+@pytest.mark.parametrize("T", [1, 2, 3, 4, 5, 8, 13, 16, 17, 31, 64])
+@pytest.mark.parametrize("U", [161, 255, 256, 330, 511])
+def test_wide_lattices_round_boundaries(oracle, T, U):
+    """Launches wider than 160 columns run the wavefront in rounds of four steps over a 16-slot operand ring and 8
+    result rows. The number of diagonals T+U takes every residue of 4 and 16 here, with fewer frames than one round, one
+    frame, and a narrow sequence (one warp) beside the wide one in the same launch."""
+    rng = np.random.default_rng(T * 1000 + U)
+    lx = np.array([T, max(1, T - 1), T], dtype=np.int32)
+    ly = np.array([U, 7, U - 33], dtype=np.int32)
+    V = 6
+    y = rng.integers(1, V, size=(3, U)).astype(np.int32)
+    rows = int((lx.astype(np.int64) * (ly + 1)).sum())
+    case = dict(x=rng.standard_normal((rows, V)).astype(np.float32), lx=lx, ly=ly, y=y, blank=0, V=V)
+    _check_fused(oracle, case)
+
+
 def test_long_form_sequence_against_oracle(oracle):
     """One sequence of the long-form workload's size (T=1200, U=300, V=512: 1900 diagonals, 301 columns = 10 compute
     and 10 helper warps in the wavefront kernel)."""
