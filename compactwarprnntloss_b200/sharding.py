@@ -30,7 +30,8 @@ def plan_shards(lx: Sequence[int], ly: Sequence[int], world: int, order: str = "
         first one done, so the shortest goes first and the gradient pass follows the gather pass without a gap
         (measured on 4 x [1250 x 300] x 512: 1.49 ms per step against 1.56), while the longest, gathered right after
         it, still has both passes to hide under. With many sequences per group a group is as slow as its longest
-        chain, and a lead of short ones buys nothing (ragged 256-sequence batch: 0.71 ms against 0.68).
+        chain, and a lead of short ones buys nothing (ragged 256-sequence batch: 0.71 ms against 0.68 with one short
+        sequence in front; 0.69-0.77 ms against 0.66 with a leading block of short sequences holding 5-27 % of the rows).
     ``order="ascending"``  ascending global index (each rank's compact rows stay in global order).
     """
     if order not in ("longest_first", "pipeline", "ascending"):
