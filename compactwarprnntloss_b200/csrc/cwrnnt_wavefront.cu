@@ -7,7 +7,8 @@
 //   alpha(t,u) = LSE(alpha(t-1,u) + blank(t-1,u), alpha(t,u-1) + label(t,u-1)),  alpha(0,0) = 0     (:59-125)
 //   beta(t,u)  = LSE(beta(t+1,u) + blank(t,u),    beta(t,u+1) + label(t,u)),     beta(T-1,U) = blank(T-1,U)  (:165-231)
 // Two kernels share the recursion. Lattices of up to 512 columns take the split-role kernel (further down): a compute
-// warp and a helper warp per 32 columns. Wider ones take the single-role kernel: the own-column operand stays in a
+// warp and a helper warp per 32 columns, meeting on one barrier per diagonal or, for wide float lattices, once per
+// round of four diagonals. Wider ones take the single-role kernel: the own-column operand stays in a
 // register, the neighbour column arrives by warp shuffle (shared memory only at warp seams), one named barrier per
 // diagonal, 1, 4 or 8 columns per thread. In both, the log-probs K1 wrote diagonal-major form one contiguous stream
 // per (sequence, direction); each thread stages its own operands, several diagonals ahead of the dependent chain,
