@@ -397,11 +397,17 @@ wavefront_kernel(WaveArgs<typename std::conditional<F64, double, float>::type> g
 // Up to 512 columns. The time of a step follows the number of instructions one warp has to issue on it (a warp on this
 // chain issues about one instruction every four to five cycles and no other warp of the sequence can take its place),
 // so the work of a 32-column group is split over two warps that run side by side on the SM's schedulers:
-//   compute warp: operands out of the shared-memory ring, neighbour value, the log-sum-exp, result into shared memory;
-//   helper warp : stages the operands `R` steps ahead (8-byte cp.async, all the index arithmetic and predicates),
-//                 and moves the previous step's results from shared memory to global memory.
-// Results pass through a double-buffered row `vbuf[2][columns]`, which also serves as the neighbour exchange (no
-// shuffles, no warp-seam special case). One named barrier per step joins all warps of the CTA.
+//   compute warp: operands out of the shared-memory ring, neighbour value, the log-sum-exp, result into shared memory
+//                 and, one step later, to global memory;
+//   helper warp : stages the operands `R` steps ahead (8-byte cp.async, all the index arithmetic and predicates) and
+//                 publishes, per ring slot, the stream offset of the diagonal it holds (`diag_base`).
+// Results pass through a double-buffered row `vbuf[2][columns]` for the neighbour exchange (no shuffles, no warp-seam
+// special case). One named barrier per step joins all warps of the CTA. The global store of a result is issued at
+// the START of the following step: the barrier waits for the warp's outstanding stores, so a store issued right
+// before it costs its whole round trip on every step (0.163 us per diagonal at 32 columns), one issued a step's
+// length ahead costs nothing (0.127-0.130; with the helper loading and storing the results instead, 0.134 - there
+// the helper's own instruction stream, about 200 cycles a step, was what the compute warp waited for). Timing-only
+// builds give the parts of a step at 32 columns: skeleton 0.016 us, log-sum-exp chain 0.065 us, barrier 0.013 us.
 // Hand-over of ring slot x % R (operands of step x): the helper's copy group for step s+2 is complete before the
 // barrier that ends step s; the compute warp reads the operands of step s+1 during step s (one step ahead, into
 // registers); the helper refills slot s % R during step s, after its last read during step s-1. Step 0's operands
@@ -415,7 +421,7 @@ template <int R, bool F64, bool BETA>
 __device__ __forceinline__ void run_direction_split(int T, int U, const double *__restrict__ lpb,
                                                     const double *__restrict__ lpl, double *__restrict__ out,
                                                     double *__restrict__ ll_out, int n_cols, int n_sync,
-                                                    double *stage, double *vbuf,
+                                                    double *stage, double *vbuf, int *diag_base,
                                                     const float4 *__restrict__ lse_tab, bool helper, int u)
 {
     const int m = U + 1;
@@ -433,9 +439,8 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
         int e = BETA ? nd - 1 : -1;
         int base = BETA ? T * m - 1 - U : 0;
         int tb = u <= U ? e - u : INT_MIN / 2;  // parked far outside every range for columns beyond U
-        int sbase[R];
         auto issue = [&](int k) {
-            sbase[k] = base;
+            if (u == 0) diag_base[k] = base;
             double *sb = st_b + k * n_cols, *sl = st_l + k * n_cols;
             if (!BETA) {
                 // step e+1 at column u needs blank(e-u, u) and label(e-u+1, u-1)
@@ -458,28 +463,16 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
 #pragma unroll
         for (int k = 0; k < R; ++k) issue(k);
         cp_async_wait<R - 2>();  // operands of steps 0 and 1 are in place
-        int tprev = u <= U ? (BETA ? nd - u : -u - 1) : INT_MIN / 2;  // frame index of this column one step ago
-        int last_base = 0;
         asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");      // start barrier: steps 0 and 1 are staged
         // second barrier: the compute warps have taken the operands of step 0 out of slot 0, which the first
         // iteration below refills
         asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
 
-        // step s: store the result of step s-1, refill slot s % R with the operands of step s+R
-        for (int s0 = 0; s0 <= nd; s0 += R) {
+        // step s: refill slot s % R with the operands of step s+R
+        for (int s0 = 0; s0 < nd; s0 += R) {
 #pragma unroll
             for (int k = 0; k < R; ++k) {
-                const int s = s0 + k;
-                if (s > nd) break;
-                // diagonal written by step s-1: alpha -> the data diagonal of step s (slot k, read before issue(k)
-                // recycles it); beta -> the data diagonal of step s-1 (remembered from the previous round)
-                const int this_base = sbase[k];
-                const int out_base = BETA ? last_base : this_base;
-                last_base = this_base;
-                // R is even and s0 a multiple of R: the parity of s is the parity of k
-                if (s >= 1 && unsigned(tprev) < unsigned(T)) out[out_base + u] = (k & 1) ? v0[u] : v1[u];
-                tprev += BETA ? -1 : 1;
-                if (s == nd) break;  // last round only drains the final result
+                if (s0 + k >= nd) break;
                 issue(k);
                 cp_async_wait<R - 2>();
                 asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
@@ -499,24 +492,36 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
     }
     double prev = (u == (BETA ? U : 0)) ? 0.0 : -INFINITY;
     const int nb_col = BETA ? (u >= U ? n_cols : u + 1) : (u == 0 ? n_cols : u - 1);
+    // frame index of this column's cell one step before step 0 (parked far outside for columns beyond U)
+    int t_prev = u <= U ? (BETA ? nd - u : -u - 1) : INT_MIN / 2;
     asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");  // start barrier: operands of steps 0 and 1 are staged
     double cur_b = st_b[0], cur_l = st_l[0];
+    int cur_base = diag_base[0], prev_base = 0;
     asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");  // slot 0 is read: the helper may refill it
     for (int s0 = 0; s0 < nd; s0 += R) {
 #pragma unroll
         for (int k = 0; k < R; ++k) {
             if (s0 + k >= nd) break;
+            // The result of the previous step goes out first, so that the store has the whole step to complete
+            // before this warp arrives at the barrier. It lies on the diagonal whose operands this step reads
+            // (alpha) / the previous step read (beta).
+            if (unsigned(t_prev) < unsigned(T)) out[(BETA ? prev_base : cur_base) + u] = prev;
+            t_prev += BETA ? -1 : 1;
             const double nxt_b = st_b[((k + 1) % R) * n_cols];
             const double nxt_l = st_l[((k + 1) % R) * n_cols];
+            const int nxt_base = diag_base[(k + 1) % R];
             const double nb = (k & 1) ? v0[nb_col] : v1[nb_col];  // the neighbour's result of the previous step
             const double v = lse2<F64>(prev + cur_b, nb + cur_l, lse_tab);
             if (k & 1) v1[u] = v; else v0[u] = v;
             prev = v;
             cur_b = nxt_b;
             cur_l = nxt_l;
+            prev_base = cur_base;
+            cur_base = nxt_base;
             asm volatile("bar.sync 1, %0;" ::"r"(n_sync) : "memory");
         }
     }
+    if (unsigned(t_prev) < unsigned(T)) out[(BETA ? prev_base : cur_base) + u] = prev;  // the last step's result
     if (!BETA) {
         if (u == U) *ll_out = prev + __ldg(lpb + int64_t(T) * m - 1);
     } else {
@@ -536,8 +541,10 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
 // latest, so one copy group per round and `wait_group 2` leave every copy between two and three rounds to land. The
 // prologue stages steps 0 .. R-Q and the first round continues from there. Rows of results live for two rounds: the
 // compute warps write row x % V again Q*2 = V steps later, after the barrier that ends the round in which the helpers
-// read it. Measured against the per-step barrier above: 0.194 vs 0.218 us per diagonal at 256 columns, 0.306 vs
-// 0.352 at 512; equal near 150 columns and a few per cent slower below (more shared memory, longer prologue). The
+// read it. Measured against the per-step barrier above: 0.194 vs 0.204 us per diagonal at 256 columns, 0.248 vs
+// 0.265 at 384, 0.306 vs 0.332 at 512; slower below about 160 columns (0.170 vs 0.164 at 151; more shared memory,
+// longer prologue). Here the helpers keep the stores: the compute warps of a wide lattice have no issue slots to
+// spare (with the stores moved to them as above: 0.202 at 256 columns, 0.321 at 512). The
 // double-precision recursion (libm exp/log1p on the chain) measured slower this way up to 384 columns (0.84 vs 0.73 us
 // per diagonal at 256) and stays on the per-step barrier.
 template <bool F64, bool BETA>
@@ -666,6 +673,7 @@ wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::t
     __shared__ double edge[2][32];
     __shared__ float4 lse_tab[F64 ? 1 : kLseNodes];
     __shared__ int last_flag;
+    __shared__ int diag_base[16];  // per ring slot: stream offset of the diagonal its operands come from
     const Workspace &w = g.w;
     if (w.status[0] & CWRNNT_ST_FATAL) return;
 
@@ -698,10 +706,11 @@ wavefront_split_kernel(WaveArgs<typename std::conditional<F64, double, float>::t
     } else {
         if (beta_dir)
             run_direction_split<R, F64, true>(T, U, w.lp_blank + off, w.lp_label + off, w.beta + off, w.ll_beta + n,
-                                              n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+                                              n_cols, n_sync, stage, vbuf, diag_base, lse_tab, is_helper, col);
         else
             run_direction_split<R, F64, false>(T, U, w.lp_blank + off, w.lp_label + off, w.alpha + off,
-                                               w.ll_alpha + n, n_cols, n_sync, stage, vbuf, lse_tab, is_helper, col);
+                                               w.ll_alpha + n, n_cols, n_sync, stage, vbuf, diag_base, lse_tab,
+                                               is_helper, col);
     }
     // the compute warps finalise (helpers are done; n_cols threads with dense ids 0..n_cols-1)
     if (is_helper) return;
@@ -738,7 +747,7 @@ static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
 
 // True when `grid` CTAs of `threads` threads and `smem` bytes of dynamic shared memory are all resident at once. The
 // rounds variant takes 2.2 times the shared memory of the per-step one; on a launch that no longer fits the device in
-// one wave the second wave costs more than the cheaper barrier saves (512 CTAs of 256 columns: 234 us against 226 us).
+// one wave the second wave costs more than the cheaper barrier saves (512 CTAs of 256 columns: 234 us against 213 us).
 static bool one_wave(int grid, int threads, size_t smem)
 {
     struct Limits { int sms = 0, smem_per_sm = 0; };
