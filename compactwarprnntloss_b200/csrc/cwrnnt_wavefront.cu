@@ -66,15 +66,19 @@ __device__ __forceinline__ void build_lse_table(float4 *tab, int tid, int n_thre
     }
 }
 
+// The step of the split-role kernels: a = own column's term (known early), nb = the neighbour's value (arrives last),
+// l = the label operand. a - (nb + l) is taken as (a - l) - nb, so that only ONE double addition stands between the
+// arrival of nb and the float correction; nb + l is needed for the result only and runs beside it.
 template <bool F64>
-__device__ __forceinline__ double lse2(double a, double b, const float4 *__restrict__ tab)
+__device__ __forceinline__ double lse2_late(double a, double l, double nb, const float4 *__restrict__ tab)
 {
+    const double b = nb + l;
     if (F64) {
         const double hi = fmax(a, b), lo = fmin(a, b);
         if (hi == -INFINITY) return hi;
         return hi + log1p(exp(lo - hi));
     }
-    const double diff = a - b;
+    const double diff = (a - l) - nb;
     const float g = fminf(fabsf(__double2float_rn(diff)), 32.0f);  // fminf drops a NaN operand
     const float q = fmaf(g, 16.0f, kLseMagic);
     const float4 t = tab[__float_as_int(q) & 0x3ff];
@@ -239,7 +243,7 @@ __device__ __forceinline__ void run_direction(int T, int U, const double *__rest
                 else
                     other = (j == C - 1) ? nb : prev[j + 1];
                 if (first) other = -INFINITY;
-                const double v = lse2<F64>(prev[j] + cur_b[j], other + cur_l[j], lse_tab);
+                const double v = lse2_late<F64>(prev[j] + cur_b[j], cur_l[j], other, lse_tab);
                 nw[j] = v;
                 if (unsigned(tcur[j]) < unsigned(T)) out[out_base + u0 + j] = v;
             }
@@ -511,7 +515,7 @@ __device__ __forceinline__ void run_direction_split(int T, int U, const double *
             const double nxt_l = st_l[((k + 1) % R) * n_cols];
             const int nxt_base = diag_base[(k + 1) % R];
             const double nb = (k & 1) ? v0[nb_col] : v1[nb_col];  // the neighbour's result of the previous step
-            const double v = lse2<F64>(prev + cur_b, nb + cur_l, lse_tab);
+            const double v = lse2_late<F64>(prev + cur_b, cur_l, nb, lse_tab);
             if (k & 1) v1[u] = v; else v0[u] = v;
             prev = v;
             cur_b = nxt_b;
@@ -647,7 +651,7 @@ __device__ __forceinline__ void run_direction_rounds(int T, int U, const double 
                     const double nxt_b = st_b[((k + 1) % R) * n_cols];
                     const double nxt_l = st_l[((k + 1) % R) * n_cols];
                     const double nb = vbuf[((k + V - 1) % V) * vstride + nb_col];
-                    const double v = lse2<F64>(prev + cur_b, nb + cur_l, lse_tab);
+                    const double v = lse2_late<F64>(prev + cur_b, cur_l, nb, lse_tab);
                     vbuf[(k % V) * vstride + u] = v;
                     prev = v;
                     cur_b = nxt_b;
