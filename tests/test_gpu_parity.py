@@ -179,6 +179,22 @@ def test_costs_only_matches_full(oracle):
     np.testing.assert_allclose(only["costs"], costs, rtol=LOSS_RTOL)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.float64])
+def test_wide_lattices_costs_only_and_other_dtypes(oracle, dtype):
+    """The wide-lattice wavefront (rounds for float-type inputs, the per-diagonal barrier for double) with 16-bit and
+    double inputs, and with beta-only CTAs (costs without gradients): 200 to 340 columns beside a narrow sequence."""
+    from tests.gpu_helpers import run_engine
+    case = ragged_case(91, 4, (9, 60), (200, 339), V=16)
+    case["ly"][1] = 5
+    rows = int((case["lx"].astype(np.int64) * (case["ly"] + 1)).sum())
+    case["x"] = np.random.default_rng(5).standard_normal((rows, 16)).astype(np.float32)
+    _check_fused(oracle, case, dtype=dtype)
+    up = _upcast(case, dtype)
+    only = run_engine(case, dtype=dtype, costs_only=True)
+    costs, _ = oracle.fused(up["x"], case["lx"], case["ly"], case["y"], 0, want_grad=False)
+    np.testing.assert_allclose(only["costs"], costs, rtol=LOSS_RTOL, atol=1e-6)
+
+
 def test_recursion_alone_on_a_gathered_workspace(oracle):
     """cwrnnt_recursion re-runs the alpha/beta wavefront and the cost step on the state a forward left behind: costs
     and loss come out bit-identical, with and without the alpha direction, and a backward may still follow."""
