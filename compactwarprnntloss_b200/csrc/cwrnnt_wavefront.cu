@@ -749,34 +749,38 @@ static cudaError_t opt_in_smem(K kernel, size_t smem, int threads)
     return opt_in_smem_impl(reinterpret_cast<const void *>(kernel), smem, threads);
 }
 
-// True when `grid` CTAs of `threads` threads and `smem` bytes of dynamic shared memory are all resident at once. The
-// rounds variant takes 2.2 times the shared memory of the per-step one; on a launch that no longer fits the device in
-// one wave the second wave costs more than the cheaper barrier saves (512 CTAs of 256 columns: 234 us against 213 us).
-static bool one_wave(int grid, int threads, size_t smem)
+// True when `grid` CTAs of `kernel` with `threads` threads and `smem` bytes of dynamic shared memory are all resident
+// at once (registers, shared memory and thread slots counted by the occupancy calculator; asked once per device and
+// launch shape). The rounds variant takes 2.2 times the shared memory of the per-step one; on a launch that no longer
+// fits the device in one wave the second wave costs more than the cheaper barrier saves (512 CTAs of 256 columns:
+// 234 us against 213 us).
+static bool one_wave(const void *kernel, int grid, int threads, size_t smem)
 {
-    struct Limits { int sms = 0, smem_per_sm = 0; };
+    struct Shape {
+        int device, threads;
+        size_t smem;
+        bool operator<(const Shape &o) const
+        {
+            return device != o.device ? device < o.device : threads != o.threads ? threads < o.threads : smem < o.smem;
+        }
+    };
     static std::mutex lock;
-    static std::map<int, Limits> seen;
+    static std::map<Shape, int64_t> resident;  // CTAs the whole device holds at once
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return false;
-    Limits lim;
-    {
-        std::lock_guard<std::mutex> hold(lock);
-        Limits &l = seen[device];
-        if (l.sms == 0) {
-            if (cudaDeviceGetAttribute(&l.sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
-                cudaDeviceGetAttribute(&l.smem_per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, device) !=
-                    cudaSuccess) {
-                l = Limits{};
-                return false;
-            }
+    std::lock_guard<std::mutex> hold(lock);
+    const Shape key{device, threads, smem};
+    auto it = resident.find(key);
+    if (it == resident.end()) {
+        int sms = 0, per_sm = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
         }
-        lim = l;
+        it = resident.emplace(key, int64_t(sms) * per_sm).first;
     }
-    const size_t per_cta = smem + 10 * 1024;  // static arrays of the kernel (8.6 KB) and the per-CTA reserve (1 KB)
-    const int by_smem = int(size_t(lim.smem_per_sm) / per_cta);
-    const int by_threads = 2048 / threads;
-    return int64_t(grid) <= int64_t(lim.sms) * (by_smem < by_threads ? by_smem : by_threads);
+    return int64_t(grid) <= it->second;
 }
 
 template <bool F64>
@@ -816,11 +820,13 @@ static cudaError_t launch_wavefront_t(const cwrnnt_problem &p, const int32_t *lx
         const size_t smem = (size_t(2 * R + 2) * half + 2) * sizeof(double);
         const size_t wide = (size_t(2 * kRoundsRing + kRoundsRows) * half + kRoundsRows) * sizeof(double);
         if constexpr (!F64) {
-            if (half > kRoundsMinCols && one_wave(grid, threads, wide)) {
-                if ((e = opt_in_smem(wavefront_split_kernel<kRoundsRing, false, true>, wide, threads)) != cudaSuccess)
-                    return e;
-                wavefront_split_kernel<kRoundsRing, false, true><<<grid, threads, wide, s>>>(g);
-                return cudaGetLastError();
+            if (half > kRoundsMinCols) {
+                auto rounds = wavefront_split_kernel<kRoundsRing, false, true>;
+                if ((e = opt_in_smem(rounds, wide, threads)) != cudaSuccess) return e;
+                if (one_wave(reinterpret_cast<const void *>(rounds), grid, threads, wide)) {
+                    rounds<<<grid, threads, wide, s>>>(g);
+                    return cudaGetLastError();
+                }
             }
         }
         if ((e = opt_in_smem(wavefront_split_kernel<R, F64, false>, smem, threads)) != cudaSuccess) return e;
